@@ -1,5 +1,5 @@
-"""A small, whole, single-GPU inference engine for Qwen3 dense (and two more designs, Gamilorn and Zatirax,
-registered beside it) on B200 (sm_100a):
+"""A small, whole, single-GPU inference engine for Qwen3 dense (and three more designs, Gamilorn, Zatirax and
+Kipezen, registered beside it) on B200 (sm_100a):
 typed configuration and registry, safetensors weights, a model put together from
 parts, a paged cache manager, one step function over mixed batches, a
 continuous-batching scheduler, sampling, and hand-written CUDA kernels.
@@ -8,10 +8,10 @@ continuous-batching scheduler, sampling, and hand-written CUDA kernels.
     out = Engine(EngineConfig(model_path=DIR)).generate([[1, 2, 3]], SamplingParams())
 """
 
-from .config import (ConfigError, EngineConfig, GamilornConfig, Qwen3Config, SamplingParams, ZatiraxConfig,
-                     preset, preset_names)
+from .config import (ConfigError, EngineConfig, GamilornConfig, KipezenConfig, Qwen3Config, SamplingParams,
+                     ZatiraxConfig, preset, preset_names)
 
-__all__ = ["Engine", "EngineConfig", "SamplingParams", "Qwen3Config", "GamilornConfig", "ZatiraxConfig", "ConfigError", "preset",
+__all__ = ["Engine", "EngineConfig", "SamplingParams", "Qwen3Config", "GamilornConfig", "ZatiraxConfig", "KipezenConfig", "ConfigError", "preset",
            "preset_names", "RequestOutput"]
 
 

@@ -4,7 +4,8 @@
 // rows, the one that prepares a latent (low-rank) key/value row, and a product per head.
 //
 // Masks (mask_kind, mask_size): 0 causal: a query at position p sees keys 0 .. p; 1 window:
-// p - size + 1 .. p; 2 chunk: floor(p / size) * size .. p (chunks counted from position 0).
+// p - size + 1 .. p, and with keep > 0 also the sequence's first keys 0 .. keep - 1 (at their true
+// positions); 2 chunk: floor(p / size) * size .. p (chunks counted from position 0).
 //
 // A page of a cache holds its keys [Hkv, page_size, Dk] and then its values [Hkv, page_size, Dv];
 // with Dv_stored == 0 nothing is stored for values and a key's first Dv elements are its value
@@ -90,6 +91,91 @@ attn_prepare_kernel(Source proj, long long row_width, T* __restrict__ q_out, T* 
     }
     Elem<T>::store(dst + d, v);
   }
+}
+
+// The same for a whole projection row at once: one block per token, which sees every head of q and k.
+// A bias (float32 over [q | k | v]) joins the projection before anything else; the RMS norm of q and
+// of k runs per head (whole == 0, weights of D elements) or over all heads of the projection at once
+// (whole == 1, weights of Hq * D and Hkv * D elements); the rotation pairs element i with i + rot/2
+// (pairs == 0) or element 2i with 2i + 1 (pairs == 1), angle = position * freq[i].
+constexpr int ROW_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+attn_prepare_row_kernel(Source proj, long long row_width, const float* __restrict__ bias, T* __restrict__ q_out,
+                        T* __restrict__ cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                        int whole, float eps, const float* __restrict__ freq, int rot, int pairs,
+                        const int* __restrict__ positions, const int* __restrict__ slot_mapping, int Hq, int Hkv,
+                        int D, int Dv, int page_size, long long num_pages) {
+  extern __shared__ float smem[];      // the row's [q | k | v] (nq + nk + nv floats), then a factor per q and k head
+  __shared__ float scratch[32];
+  pdl_prologue(proj.p);
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = Hq * D, nk = Hkv * D, nv = Hkv * Dv;
+  float* x = smem;
+  float* factor = smem + nq + nk + nv;
+  const long long row = (long long)t * row_width;
+  for (int i = threadIdx.x; i < nq + nk + nv; i += ROW_THREADS) {
+    float v = source_load(proj, row + i);
+    if (bias != nullptr) v = __fadd_rn(v, bias[i]);
+    x[i] = round_to<T>(v);
+  }
+  __syncthreads();
+  if (q_w != nullptr) {
+    if (whole) {
+      float sq = 0.f, sk = 0.f;
+      for (int i = threadIdx.x; i < nq; i += ROW_THREADS) sq = __fmaf_rn(x[i], x[i], sq);
+      for (int i = threadIdx.x; i < nk; i += ROW_THREADS) sk = __fmaf_rn(x[nq + i], x[nq + i], sk);
+      const float rq = 1.0f / sqrtf(block_sum(sq, scratch) / (float)nq + eps);
+      const float rk = 1.0f / sqrtf(block_sum(sk, scratch) / (float)nk + eps);
+      for (int i = threadIdx.x; i < nq; i += ROW_THREADS) x[i] = x[i] * rq * q_w[i];
+      for (int i = threadIdx.x; i < nk; i += ROW_THREADS) x[nq + i] = x[nq + i] * rk * k_w[i];
+    } else {
+      for (int s = warp; s < Hq + Hkv; s += ROW_THREADS / 32) {
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) ss = __fmaf_rn(x[s * D + d], x[s * D + d], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) factor[s] = 1.0f / sqrtf(ss / (float)D + eps);
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < nq + nk; i += ROW_THREADS) {
+        const int s = i / D, d = i - s * D;
+        x[i] = x[i] * factor[s] * (s < Hq ? q_w[d] : k_w[d]);
+      }
+    }
+    __syncthreads();
+  }
+  long long page_at = -1;
+  int off = 0;
+  if (cache != nullptr) {
+    const int slot = slot_mapping[t];
+    if (slot >= 0 && slot < num_pages * page_size) {
+      page_at = (long long)(slot / page_size) * Hkv * page_size * (D + Dv);
+      off = slot % page_size;
+    }
+  }
+  const float pos = (float)positions[t];
+  const int half = rot / 2;
+  for (int i = threadIdx.x; i < nq + nk; i += ROW_THREADS) {
+    const int s = i / D, d = i - s * D;
+    float v = x[i];
+    if (d < rot) {
+      // the element's partner, its frequency, and whether it is the pair's first element
+      const bool first = pairs ? (d & 1) == 0 : d < half;
+      const int other = pairs ? (d ^ 1) : (first ? d + half : d - half);
+      const float a = __fmul_rn(pos, freq[pairs ? d >> 1 : (first ? d : d - half)]);
+      const float c = cosf(a), sn = sinf(a), o = x[s * D + other];
+      v = first ? __fmaf_rn(v, c, -__fmul_rn(o, sn)) : __fmaf_rn(v, c, __fmul_rn(o, sn));
+    }
+    if (s < Hq) Elem<T>::store(q_out + (long long)t * nq + i, v);
+    else if (page_at >= 0) Elem<T>::store(cache + page_at + ((long long)(s - Hq) * page_size + off) * D + d, v);
+  }
+  if (page_at >= 0)
+    for (int i = threadIdx.x; i < nv; i += ROW_THREADS) {
+      const int s = i / Dv, d = i - s * Dv;
+      Elem<T>::store(cache + page_at + (long long)Hkv * page_size * D + ((long long)s * page_size + off) * Dv + d,
+                     x[nq + nk + i]);
+    }
 }
 
 // ---- a latent key/value row ------------------------------------------------------------------
@@ -203,7 +289,7 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
                         const int* __restrict__ block_table, int max_blocks,
                         const int* __restrict__ token_seq, const int* __restrict__ positions,
                         int T_tokens, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
-                        float scale, int mask_kind, int mask_size, const float* __restrict__ sink,
+                        float scale, int mask_kind, int mask_size, int keep, const float* __restrict__ sink,
                         Source gate, long long gate_row, long long gate_col) {
   extern __shared__ float smem[];
   pdl_prologue(q, cache, block_table, token_seq, positions, gate.p);
@@ -228,9 +314,12 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
   const size_t page_elems = (size_t)Hkv * page_size * (Dk + Dv_stored);
   const size_t values_at = (size_t)Hkv * page_size * Dk;
 
-  for (int k0 = (first / 32) * 32; k0 <= pos; k0 += 32) {
+  // kept first keys that the window has passed: their tiles come first, then the window's
+  const int kept_end = keep < first ? keep : first;
+  const int window_from = (first / 32) * 32 > (kept_end + 31) / 32 * 32 ? (first / 32) * 32 : (kept_end + 31) / 32 * 32;
+  for (int k0 = kept_end > 0 ? 0 : window_from; k0 <= pos; k0 = (k0 + 32 >= kept_end && k0 + 32 < window_from) ? window_from : k0 + 32) {
     const int key = k0 + lane;
-    const bool visible = key >= first && key <= pos;
+    const bool visible = (key >= first || key < kept_end) && key <= pos;
     float s = NEG_BIG;
     const T* vrow = nullptr;
     if (visible) {
@@ -295,14 +384,14 @@ template <typename T>
 int launch_masked_attention(const void* q, void* out, const void* cache, const int* block_table,
                             int max_blocks, const int* token_seq, const int* positions, int T_tokens, int Hq,
                             int Hkv, int Dk, int Dv, int Dv_stored, int page_size, float scale, int mask_kind,
-                            int mask_size, const float* sink, Source gate, long long gate_row,
+                            int mask_size, int keep, const float* sink, Source gate, long long gate_row,
                             long long gate_col, cudaStream_t st) {
   const int blocks = ceil_div_host((long long)T_tokens * Hq, WARPS);
   const size_t smem = (size_t)WARPS * Dk * sizeof(float);
 #define DIB_MA(NV)                                                                                       \
   dib_launch(masked_attention_kernel<T, NV>, dim3(blocks), dim3(WARPS * 32), smem, st, (const T*)q, (T*)out, \
              (const T*)cache, block_table, max_blocks, token_seq, positions, T_tokens, Hq, Hkv, Dk, Dv,   \
-             Dv_stored, page_size, scale, mask_kind, mask_size, sink, gate, gate_row, gate_col)
+             Dv_stored, page_size, scale, mask_kind, mask_size, keep, sink, gate, gate_row, gate_col)
   if (Dv <= 64) DIB_MA(2);
   else if (Dv <= 128) DIB_MA(4);
   else if (Dv <= 256) DIB_MA(8);
@@ -337,6 +426,43 @@ int dib_attn_prepare(const void* proj, int kind, int splits, long long stride, l
                (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, q_w, k_w, eps, freq, rot, positions, slot_mapping, T,
                Hq, Hkv, D, Dv, page_size, num_pages);
   else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// The form that takes a row at once (attn_prepare_row_kernel): a bias, a norm over the whole projection,
+// interleaved rotation pairs.  bias null: none.
+int dib_attn_prepare_row(const void* proj, int kind, int splits, long long stride, long long row_width,
+                         const float* bias, void* q_out, void* cache, const float* q_w, const float* k_w, int whole,
+                         float eps, const float* freq, int rot, int pairs, const int* positions,
+                         const int* slot_mapping, int T, int Hq, int Hkv, int D, int Dv, int page_size,
+                         long long num_pages, int dtype, cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  if (D < 1 || Dv < 1 || Hq < 1 || Hkv < 1 || rot < 0 || rot > D || rot % 2 || page_size < 1) return DIB_BAD_SIZE;
+  if (freq == nullptr) rot = 0;
+  const size_t smem = sizeof(float) * ((size_t)Hq * D + (size_t)Hkv * (D + Dv) + Hq + Hkv);
+  if (smem > 200 * 1024) return DIB_BAD_SIZE;
+  const Source src = make_source(proj, kind, splits, stride);
+  static DeviceOnce once32, once16;
+  if (dtype == 0) {
+    if (smem > 48 * 1024 && !once32.done()) {
+      if (cudaFuncSetAttribute(attn_prepare_row_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               200 * 1024) != cudaSuccess) return DIB_LAUNCH_FAILED;
+      once32.mark();
+    }
+    dib_launch(attn_prepare_row_kernel<float>, dim3(T), dim3(ROW_THREADS), smem, st, src, row_width, bias,
+               (float*)q_out, (float*)cache, q_w, k_w, whole, eps, freq, rot, pairs, positions, slot_mapping, Hq, Hkv,
+               D, Dv, page_size, num_pages);
+  } else if (dtype == 1) {
+    if (smem > 48 * 1024 && !once16.done()) {
+      if (cudaFuncSetAttribute(attn_prepare_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               200 * 1024) != cudaSuccess) return DIB_LAUNCH_FAILED;
+      once16.mark();
+    }
+    dib_launch(attn_prepare_row_kernel<__nv_bfloat16>, dim3(T), dim3(ROW_THREADS), smem, st, src, row_width, bias,
+               (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, q_w, k_w, whole, eps, freq, rot, pairs, positions,
+               slot_mapping, Hq, Hkv, D, Dv, page_size, num_pages);
+  } else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -409,20 +535,21 @@ int dib_sigmoid_gate_(void* x, const void* gate, int kind, int splits, long long
 int dib_masked_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
                              const int* positions, const int* seq_lens, const int* cu_q_lens, const int* tiles,
                              int num_tiles, const float* sink, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
-                             float scale, int mask_kind, int mask_size, const void* gate, int gate_kind,
+                             float scale, int mask_kind, int mask_size, int keep, const void* gate, int gate_kind,
                              int gate_splits, long long gate_stride, long long gate_row, long long gate_col,
                              int rows, float* partial_o, float* partial_ml, int chunk_tiles, int max_chunks,
                              int num_tokens, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (Dk < 16 || Dk % 16 || Dv < 16 || Dv % 16 || Dv > 256 || Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > rows ||
       (rows != 64 && rows != 128) || page_size < 1 || mask_kind < 0 || mask_kind > 2 ||
-      (mask_kind > 0 && mask_size < 1) || (Dv_stored != 0 && Dv_stored != Dv) || (Dv_stored == 0 && Dv > Dk) ||
+      (mask_kind > 0 && mask_size < 1) || keep < 0 || (keep > 0 && mask_kind != 1) ||
+      (Dv_stored != 0 && Dv_stored != Dv) || (Dv_stored == 0 && Dv > Dk) ||
       num_tiles > 1 << 30 || Hkv > 65535 || max_chunks > 65535 || (partial_o != nullptr && chunk_tiles < 1))
     return DIB_BAD_SIZE;
   const Source g = make_source(gate, gate_kind, gate_splits, gate_stride);
 #define DIB_MAM(NV, ROWS)                                                                                    \
   return ma_mma::launch<NV, ROWS>(q, out, cache, block_table, max_blocks, positions, seq_lens, cu_q_lens, tiles, num_tiles, \
-                                  sink, Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, g, \
+                                  sink, Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, keep, g, \
                                   gate_row, gate_col, partial_o, partial_ml, chunk_tiles, max_chunks, num_tokens, st)
   const int nv = (Dv + 63) / 64;
   if (rows == 64) {
@@ -442,24 +569,24 @@ int dib_masked_attention_mma(const void* q, void* out, const void* cache, const 
 // with rows gate_row elements apart.  Dv_stored 0: a key's first Dv elements are its value.
 int dib_masked_attention(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
                          const int* token_seq, const int* positions, int T, int Hq, int Hkv, int Dk, int Dv,
-                         int Dv_stored, int page_size, float scale, int mask_kind, int mask_size,
+                         int Dv_stored, int page_size, float scale, int mask_kind, int mask_size, int keep,
                          const float* sink, const void* gate, int gate_kind, int gate_splits,
                          long long gate_stride, long long gate_row, long long gate_col, int dtype,
                          cudaStream_t st) {
   if (T == 0) return DIB_OK;
   if (Dk < 1 || Dk > 2048 || Dv < 1 || Dv > 1024 || Hkv < 1 || Hq % Hkv != 0 || page_size < 1 ||
-      mask_kind < 0 || mask_kind > 2 || (mask_kind > 0 && mask_size < 1) ||
+      mask_kind < 0 || mask_kind > 2 || (mask_kind > 0 && mask_size < 1) || keep < 0 || (keep > 0 && mask_kind != 1) ||
       (Dv_stored != 0 && Dv_stored != Dv) || (Dv_stored == 0 && Dv > Dk))
     return DIB_BAD_SIZE;
   const Source g = make_source(gate, gate_kind, gate_splits, gate_stride);
   if (dtype == 0)
     return launch_masked_attention<float>(q, out, cache, block_table, max_blocks, token_seq, positions, T, Hq,
-                                          Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, sink, g,
+                                          Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, keep, sink, g,
                                           gate_row, gate_col, st);
   if (dtype == 1)
     return launch_masked_attention<__nv_bfloat16>(q, out, cache, block_table, max_blocks, token_seq, positions, T,
                                                   Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind,
-                                                  mask_size, sink, g, gate_row, gate_col, st);
+                                                  mask_size, keep, sink, g, gate_row, gate_col, st);
   return DIB_BAD_DTYPE;
 }
 

@@ -42,6 +42,13 @@ __device__ __forceinline__ int first_seen(int pos, int mask_kind, int mask_size)
   if (mask_kind == 2) return pos > 0 ? pos / mask_size * mask_size : 0;
   return 0;
 }
+// A window mask may keep the sequence's first `keep` keys visible too.  Their tiles come first in a
+// row's walk: the key tiles 0 .. kept_tiles - 1 that lie wholly before the window's first tile, then
+// the window's tiles.
+__device__ __forceinline__ int kept_tiles(int keep, int first_window_tile) {
+  const int n = (keep + KT - 1) / KT;
+  return n < first_window_tile ? n : first_window_tile;
+}
 
 // tiles: int32 [n][3] = (sequence of the step, first token of the tile among the sequence's new tokens,
 // tokens at most).  Where the sequence's tokens lie in the step and how many it really brings is read
@@ -54,7 +61,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
                             const int* block_table, int bt_width, const int* positions, const int* seq_lens,
                             const int* cu_q_lens, const int* tiles, const float* sink, int Hq, int Hkv, int D,
                             int VD, int VD_stored,
-                            int page_size, float scale, int mask_kind, int mask_size, Source gate,
+                            int page_size, float scale, int mask_kind, int mask_size, int keep, Source gate,
                             long long gate_row, long long gate_col, float* partial_o, float* partial_ml,
                             int chunk_tiles, int max_chunks) {
   extern __shared__ __align__(16) unsigned char mam_smem[];
@@ -82,7 +89,9 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
   const long long page_elems = (long long)Hkv * page_size * (D + VD_stored);
 
   const int t_first = first_seen(pos0, mask_kind, mask_size) / KT, t_last = pos_last / KT;
-  const int n_tiles = t_last - t_first + 1;
+  const int n_kept = kept_tiles(keep, t_first);
+  const int n_tiles = n_kept + t_last - t_first + 1;
+  auto tile_at = [&](int it) { return it < n_kept ? it : t_first + it - n_kept; };   // walk step -> key tile
   const bool chunked = partial_o != nullptr;
   const int chunk = chunked ? blockIdx.z : 0;
   const int it_begin = chunked ? chunk * chunk_tiles : 0;
@@ -99,7 +108,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
   const int vchunks = VD / 8;
   auto find_rows = [&](int it) {          // by the first KT threads, for tile `it` (if there is one)
     if (threadIdx.x < KT && it < it_end) {
-      const int j = (t_first + it) * KT + threadIdx.x;
+      const int j = tile_at(it) * KT + threadIdx.x;
       long long ko = -1, vo = -1;
       if (j < kv_len) {
         // (a key beyond the table's width, a padding sequence's, reads page 0)
@@ -166,10 +175,10 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
       __pipeline_wait_prior(0);
     }
     __syncthreads();
-    const int k0 = (t_first + it) * KT;
+    const int k0 = tile_at(it) * KT;
     // does any row of this warp see a key of this tile?  (a row's first key never lies before an
     // earlier row's)
-    const bool needed = warp_has_rows && k0 <= wpos_last && k0 + KT - 1 >= wlo_first;
+    const bool needed = warp_has_rows && k0 <= wpos_last && (k0 + KT - 1 >= wlo_first || k0 < keep);
     if (needed) {
       const __nv_bfloat16* kd = Ks + stage * KT * qs;
       const __nv_bfloat16* vd = Vs + stage * KT * vs;
@@ -196,7 +205,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
         for (int e = 0; e < 4; ++e) {
           const int h = e >> 1;
           const int j = k0 + n * 8 + tig * 2 + (e & 1);
-          const bool sees = j <= row_pos[h] && j >= row_lo[h];
+          const bool sees = j <= row_pos[h] && (j >= row_lo[h] || j < keep);
           s[n][e] = sees ? s[n][e] * scale_log2 : MA_NEG_BIG;
           mx[h] = fmaxf(mx[h], s[n][e]);
         }
@@ -303,12 +312,14 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
 // A token at position p has ceil(tiles(p) / chunk_tiles) chunks, tiles(p) as the kernel above counts.
 __global__ void masked_attention_merge_kernel(const float* partial_o, const float* partial_ml, __nv_bfloat16* out,
                                               const int* positions, const float* sink, int Hq, int VD,
-                                              int mask_kind, int mask_size, Source gate, long long gate_row,
-                                              long long gate_col, int chunk_tiles, int max_chunks) {
+                                              int mask_kind, int mask_size, int keep, Source gate,
+                                              long long gate_row, long long gate_col, int chunk_tiles,
+                                              int max_chunks) {
   pdl_prologue(partial_o, partial_ml, gate.p);
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
-  const int n_tiles = pos / KT - first_seen(pos, mask_kind, mask_size) / KT + 1;
+  const int t_first = first_seen(pos, mask_kind, mask_size) / KT;
+  const int n_tiles = kept_tiles(keep, t_first) + pos / KT - t_first + 1;
   int chunks = (n_tiles + chunk_tiles - 1) / chunk_tiles;
   if (chunks > max_chunks) chunks = max_chunks;
   const long long row = (long long)t * Hq + h;
@@ -346,7 +357,7 @@ template <int NV16, int ROWS>
 static int launch(const void* q, void* out, const void* cache, const int* block_table, int bt_width,
                   const int* positions, const int* seq_lens, const int* cu_q_lens, const int* tiles, int num_tiles,
                   const float* sink, int Hq, int Hkv, int D, int VD, int VD_stored, int page_size, float scale, int mask_kind,
-                  int mask_size, Source gate, long long gate_row, long long gate_col, float* partial_o,
+                  int mask_size, int keep, Source gate, long long gate_row, long long gate_col, float* partial_o,
                   float* partial_ml, int chunk_tiles, int max_chunks, int num_tokens, cudaStream_t st) {
   const size_t smem = smem_bytes(D, VD, VD_stored, ROWS);
   if (smem > MAX_DYNAMIC_SMEM) return DIB_BAD_SIZE;
@@ -361,13 +372,13 @@ static int launch(const void* q, void* out, const void* cache, const int* block_
   dib_launch(masked_attention_mma_kernel<NV16, ROWS>, dim3(num_tiles, Hkv, chunked ? max_chunks : 1), dim3(ROWS * 2),
              smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table,
              bt_width, positions, seq_lens, cu_q_lens, tiles, sink, Hq, Hkv, D, VD, VD_stored, page_size, scale, mask_kind,
-             mask_size, gate, gate_row, gate_col, chunked ? partial_o : (float*)nullptr,
+             mask_size, keep, gate, gate_row, gate_col, chunked ? partial_o : (float*)nullptr,
              chunked ? partial_ml : (float*)nullptr, chunk_tiles, max_chunks);
   DIB_CHECK_LAUNCH();
   if (chunked) {
     dib_launch(masked_attention_merge_kernel, dim3(num_tokens, Hq), dim3(VD >= 128 ? 128 : 64), 0, st,
                (const float*)partial_o, (const float*)partial_ml, (__nv_bfloat16*)out, positions, sink, Hq, VD,
-               mask_kind, mask_size, gate, gate_row, gate_col, chunk_tiles, max_chunks);
+               mask_kind, mask_size, keep, gate, gate_row, gate_col, chunk_tiles, max_chunks);
     DIB_CHECK_LAUNCH();
   }
   return DIB_OK;

@@ -31,8 +31,8 @@ __global__ void embed_scale_kernel(const void* table, int dtype, const int* ids,
 
 // One block per row: residual[row] += x[row] / sqrt(mean(x[row]^2) + eps_x) * wx (+ bias), the
 // normed output of the part before added to the stream without being rounded; then, when out is
-// given, out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps) * w.  x null: only the bias
-// is added.  VPT > 0: a thread keeps its VPT elements of the row in registers (W <= VPT * blockDim.x),
+// given, out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps) * w (w null: out[row] =
+// residual[row], not normed).  x null: only the bias is added.  VPT > 0: a thread keeps its VPT elements of the row in registers (W <= VPT * blockDim.x),
 // so the row is read once; VPT == 0: any width, the row is read again for every pass.  Both add a
 // row's squares in the same order (a thread its own elements in ascending order, then the block's sum).
 template <int VPT>
@@ -90,6 +90,19 @@ __global__ void stream_normed_add_kernel(float* residual, Source x, const float*
     }
   }
   if (out == nullptr) return;
+  if (w == nullptr) {
+    // no norm: out is the updated stream itself in out's type
+    if (VPT > 0) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < W) store_as(out, out_dtype, base + c, rv[i]);
+      }
+    } else {
+      for (int c = threadIdx.x; c < W; c += blockDim.x) store_as(out, out_dtype, base + c, residual[base + c]);
+    }
+    return;
+  }
   const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
   if (VPT > 0) {
 #pragma unroll

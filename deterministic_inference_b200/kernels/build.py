@@ -43,6 +43,8 @@ SOURCES = {
     "sigmoid_attention": "sigmoid_attention.cu",
     "delta_rule": "delta_rule.cu",
     "masked_attention": "masked_attention.cu",
+    "linear_recurrence": "linear_recurrence.cu",
+    "routed_experts": "routed_experts.cu",
 }
 HEADERS = ("common.cuh", "attention_merge.cuh")
 # further headers a library includes
@@ -52,8 +54,10 @@ EXTRA_HEADERS = {
     "attention_prefill_tc": ("attention_bf16_kernels.cuh",),
     "stream_f32": ("source.cuh",),
     "sigmoid_attention": ("source.cuh", "sigmoid_attention_mma.cuh"),
-    "delta_rule": ("source.cuh",),
-    "masked_attention": ("source.cuh", "masked_attention_mma.cuh"),
+    "delta_rule": ("source.cuh", "conv_tail.cuh"),
+    "masked_attention": ("source.cuh", "masked_attention_mma.cuh", "sigmoid_attention_mma.cuh"),
+    "linear_recurrence": ("source.cuh", "conv_tail.cuh"),
+    "routed_experts": ("source.cuh",),
 }
 
 NVCC_FLAGS = [

@@ -788,8 +788,8 @@ def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_
 def stream_add_(stream: torch.Tensor, term=None, bias=None, norm_weight=None, norm_eps: float = 0.0,
                 out=None) -> torch.Tensor:
     """In place, float32: stream += term (a ``NormedTerm``: computed here, never rounded) + bias (a
-    float32 vector added to every row); with ``out`` also out = RMSNorm(stream) * norm_weight.
-    Returns the stream."""
+    float32 vector added to every row); with ``out`` also out = RMSNorm(stream) * norm_weight (no
+    ``norm_weight``: out = the stream in out's type).  Returns the stream."""
     _need(stream, "stream", torch.float32, 2)
     rows, w = stream.shape
     src, wx, eps_x = (c_void_p(0), c_int(0), c_int(1), c_longlong(0)), None, 0.0
@@ -803,13 +803,27 @@ def stream_add_(stream: torch.Tensor, term=None, bias=None, norm_weight=None, no
         if bias.shape[0] != w:
             raise KernelError(f"stream_add_: bias has {bias.shape[0]} elements, rows have {w}")
     if out is not None:
-        _need(norm_weight, "norm_weight", torch.float32, 1)
+        # (no norm weight: out is the stream itself in out's type, not normed)
+        if norm_weight is not None:
+            _need(norm_weight, "norm_weight", torch.float32, 1)
         _need(out, "out", None, 2)
     st = _lib("stream_f32").dib_stream_normed_add(
         _ptr(stream), *src, _ptr(wx), c_float(eps_x), _ptr(bias), _ptr(norm_weight), _ptr(out),
         c_int(_DT[out.dtype] if out is not None else 0), c_int(rows), c_int(w), c_float(norm_eps), _stream())
     _check(st, "stream_add_", f"row width {w}")
     return stream
+
+
+def stream_read(stream: torch.Tensor, term, out_dtype) -> torch.Tensor:
+    """The float32 residual stream as the next sublayer reads it: first stream += term in place (a
+    ``NormedTerm`` computed in float32 and never rounded, or None), then the stream itself in
+    ``out_dtype`` (float32: the stream, no copy)."""
+    _need(stream, "stream", torch.float32, 2)
+    if out_dtype == torch.float32:
+        return stream if term is None else stream_add_(stream, term)
+    out = torch.empty(stream.shape, dtype=out_dtype, device=stream.device)
+    stream_add_(stream, term, out=out)
+    return out
 
 
 def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
@@ -1036,10 +1050,10 @@ def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: 
     _check(st, "delta_rule(prepare)", f"heads {num_heads} of {head_dim}, rank {lora_rank}")
     o = torch.empty(t, num_heads, head_dim, dtype=torch.float32, device=dev)
     for form, first, count in delta_rule_forms(step):
-        st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), _ptr(o),
-                                      c_void_p(step.cu_q_lens.data_ptr() + 4 * first),
+        st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), c_longlong(num_heads * head_dim * head_dim),
+                                      _ptr(o), c_void_p(step.cu_q_lens.data_ptr() + 4 * first),
                                       c_void_p(step.state_slots.data_ptr() + 4 * first), c_int(count),
-                                      c_int(num_heads), c_int(head_dim), c_int(form), _stream())
+                                      c_int(num_heads), c_int(head_dim), c_int(head_dim), c_int(form), _stream())
         _check(st, "delta_rule(recurrence)", f"heads of {head_dim} (at most 256)")
     out = torch.empty(t, hd, dtype=out_dtype, device=dev)
     st = lib.dib_delta_output(_ptr(o), *src, _ptr(norm_weight), _ptr(out), c_int(_DT[out_dtype]), c_int(t),
@@ -1047,6 +1061,192 @@ def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: 
     _check(st, "delta_rule(output)")
     return out
 
+
+
+
+# ---------------------------------------------------------------- gated delta rule
+
+def gated_delta_rule(proj, conv_weight: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                     norm_weight: torch.Tensor, state: torch.Tensor, step, num_heads: int, num_kv_heads: int,
+                     head_dim: int, v_head_dim: int, taps: int, key_eps: float, norm_eps: float,
+                     out_dtype) -> torch.Tensor:
+    """The gated delta rule over every sequence's tokens of the step: [T, H * E] in ``out_dtype``.
+    ``proj`` rows are [q: G * D | k: G * D | v: H * E | g: H * E | b: H | a: H | padding].  q, k and v pass
+    a causal convolution per channel (``conv_weight`` float32 [2 G D + H E, taps], the last tap the
+    current token's; the inputs before the step's first token come from the state's tail) and silu;
+    q and k become unit vectors per head (``key_eps`` inside the root), q times D^(-1/2); beta =
+    sigmoid(b), decay = exp(-exp(a_log) * softplus(a + dt_bias)); per head S <- decay S,
+    u = beta (v - S^T k), S <- S + k u^T, o = S^T q; then o over its root mean square (``norm_eps``),
+    times ``norm_weight`` [E], times silu(g).  ``state`` float32 [slots, H D E + (taps - 1) channels]:
+    the heads' states, then the convolutions' last taps - 1 inputs (rows ``step.state_slots``)."""
+    t, width = proj.shape
+    h, g, d, e = num_heads, num_kv_heads, head_dim, v_head_dim
+    chan = 2 * g * d + h * e
+    if width < chan + h * e + 2 * h:
+        raise KernelError(f"gated_delta_rule: projection rows of {width}, expected at least {chan + h * e + 2 * h}")
+    _need(conv_weight, "conv_weight", torch.float32, 2)
+    _need(a_log, "a_log", torch.float32, 1)
+    _need(dt_bias, "dt_bias", torch.float32, 1)
+    _need(norm_weight, "norm_weight", torch.float32, 1)
+    _need(state, "state", torch.float32, 2)
+    if tuple(conv_weight.shape) != (chan, taps) or a_log.shape[0] != h or dt_bias.shape[0] != h \
+            or norm_weight.shape[0] != e or state.shape[1] != h * d * e + (taps - 1) * chan or h % g:
+        raise KernelError("gated_delta_rule: a weight or the state does not fit the head counts and sizes")
+    lib = _lib("delta_rule")
+    src = _source_args(proj)
+    dev = state.device
+    slot_stride, tail_at = state.shape[1], h * d * e
+    packed = torch.empty(t, h, 5 * d + e, dtype=torch.float32, device=dev)
+    st = lib.dib_gated_delta_prepare(*src, c_longlong(width), _ptr(conv_weight), _ptr(a_log), _ptr(dt_bias),
+                                     _ptr(state), c_longlong(slot_stride), c_longlong(tail_at), _ptr(step.token_seq),
+                                     _ptr(step.cu_q_lens), _ptr(step.state_slots), _ptr(packed), c_int(t), c_int(h),
+                                     c_int(g), c_int(d), c_int(e), c_int(taps), c_float(key_eps), _stream())
+    _check(st, "gated_delta_rule(prepare)", f"heads {h}/{g} of {d}/{e}, {taps} taps")
+    o = torch.empty(t, h, e, dtype=torch.float32, device=dev)
+    for form, first, count in delta_rule_forms(step):
+        st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), c_longlong(slot_stride), _ptr(o),
+                                      c_void_p(step.cu_q_lens.data_ptr() + 4 * first),
+                                      c_void_p(step.state_slots.data_ptr() + 4 * first), c_int(count),
+                                      c_int(h), c_int(d), c_int(e), c_int(form), _stream())
+        _check(st, "gated_delta_rule(recurrence)", f"heads of {d}/{e} (at most 256)")
+    out = torch.empty(t, h * e, dtype=out_dtype, device=dev)
+    st = lib.dib_gated_delta_output(_ptr(o), *src, c_longlong(width), _ptr(norm_weight), _ptr(out),
+                                    c_int(_DT[out_dtype]), _ptr(state), c_longlong(slot_stride), c_longlong(tail_at),
+                                    _ptr(step.cu_q_lens), _ptr(step.state_slots), c_int(t), c_int(step.num_seqs),
+                                    c_int(h), c_int(g), c_int(d), c_int(e), c_int(taps), c_float(norm_eps), _stream())
+    _check(st, "gated_delta_rule(output)", kernels=2 if taps > 1 else 1)
+    return out
+
+
+# ---------------------------------------------------------------- gated linear recurrent unit
+
+def gated_linear_recurrence(proj, bias: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor,
+                            gates: torch.Tensor, gate_bias: torch.Tensor, neg_rate: torch.Tensor,
+                            state: torch.Tensor, step, width: int, blocks: int, taps: int, out_dtype) -> torch.Tensor:
+    """[T, C] in ``out_dtype``: S_t * gelu_tanh(y_t) of the recurrent unit over every sequence's tokens
+    of the step.  ``proj`` rows are [y: C | x: C], ``bias`` float32 [2 C] is added to them.  u = the
+    causal convolution of x per channel (``conv_weight`` float32 [C, taps], the last tap the current
+    token's, plus ``conv_bias``; the inputs before the step's first token come from the state's tail).
+    In each of the ``blocks`` equal parts of u: r = sigmoid(u_b R_b + c_b), i = sigmoid(u_b I_b + d_b)
+    with ``gates`` float32 [2, blocks, in, out] = (R, I) and ``gate_bias`` [2, C]; a = exp(r *
+    neg_rate), S_t = a S_(t-1) + sqrt(1 - a^2) * i * u.  ``state`` float32 [slots, taps * C]: S, then the
+    convolution's last taps - 1 inputs (rows ``step.state_slots``)."""
+    t, got = proj.shape
+    c = int(width)
+    per = c // blocks
+    for v, name, shape in ((bias, "bias", (2 * c,)), (conv_weight, "conv_weight", (c, taps)),
+                           (conv_bias, "conv_bias", (c,)), (gates, "gates", (2, blocks, per, per)),
+                           (gate_bias, "gate_bias", (2, c)), (neg_rate, "neg_rate", (c,))):
+        _need(v, name, torch.float32)
+        if tuple(v.shape) != shape:
+            raise KernelError(f"gated_linear_recurrence: {name} of shape {tuple(v.shape)}, expected {shape}")
+    _need(state, "state", torch.float32, 2)
+    if got != 2 * c or state.shape[1] != taps * c or c % blocks:
+        raise KernelError(f"gated_linear_recurrence: rows of {got} and state rows of {state.shape[1]} for "
+                          f"{c} channels and {taps} taps")
+    lib = _lib("linear_recurrence")
+    src = _source_args(proj)
+    dev = state.device
+    u = torch.empty(t, c, dtype=torch.float32, device=dev)
+    st = lib.dib_glr_conv(*src, _ptr(bias), _ptr(conv_weight), _ptr(conv_bias), _ptr(state), _ptr(step.token_seq),
+                          _ptr(step.cu_q_lens), _ptr(step.state_slots), _ptr(u), c_int(t), c_int(c), c_int(taps),
+                          _stream())
+    _check(st, "gated_linear_recurrence(convolution)", f"{c} channels, {taps} taps")
+    decay_in = torch.empty(2, t, c, dtype=torch.float32, device=dev)
+    st = lib.dib_glr_gates(_ptr(u), _ptr(gates), _ptr(gate_bias), _ptr(neg_rate), _ptr(decay_in), c_int(t), c_int(c),
+                           c_int(blocks), _stream())
+    _check(st, "gated_linear_recurrence(gates)", f"{c} channels in {blocks} blocks")
+    out = torch.empty(t, c, dtype=out_dtype, device=dev)
+    st = lib.dib_glr_scan(_ptr(decay_in), *src, _ptr(bias), _ptr(state), _ptr(step.cu_q_lens), _ptr(step.state_slots),
+                          _ptr(out), c_int(_DT[out_dtype]), c_int(step.num_seqs), c_int(t), c_int(c), c_int(taps),
+                          _stream())
+    _check(st, "gated_linear_recurrence(scan)")
+    return out
+
+
+# ---------------------------------------------------------------- routed experts
+
+# rows of an expert's tile in the grouped products (every expert's rows are filled up to whole tiles):
+# the small tile, and the large one for steps that bring an expert EXPERT_TILE_ROWS_LARGE rows on average.
+# A row's bits do not depend on the tile it is computed in.
+EXPERT_TILE_ROWS = 16
+EXPERT_TILE_ROWS_LARGE = 64
+
+
+def route_experts(logits, correction: torch.Tensor, num_experts: int, top: int, group_count: int,
+                  group_keep: int, scale: float, eps: float):
+    """(int32 [T, top] chosen experts, float32 [T, top] their weights).  ``logits`` [T, >= E] (a float32
+    tensor or split sums; columns from E on are not the router's): s = sigmoid(logits); the choice is
+    made on s + correction: the experts form ``group_count`` groups of neighbours, a group's score is
+    the sum of its two largest choice scores, the ``group_keep`` best groups stay, and of their experts
+    the ``top`` largest choice scores win (ties: the lower index).  Weights: s of the chosen over
+    their sum (+ eps), times ``scale``."""
+    t, row = logits.shape
+    _need(correction, "correction", torch.float32, 1)
+    if correction.shape[0] != num_experts or row < num_experts or num_experts % group_count \
+            or not 1 <= group_keep <= group_count or not 1 <= top <= group_keep * (num_experts // group_count):
+        raise KernelError(f"route_experts: {num_experts} experts, rows of {row}, {group_count} groups, "
+                          f"{group_keep} kept, {top} chosen")
+    ids = torch.empty(t, top, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(t, top, dtype=torch.float32, device=logits.device)
+    st = _lib("routed_experts").dib_moe_route(*_source_args(logits), c_longlong(row), _ptr(correction), _ptr(ids),
+                                              _ptr(weights), c_int(t), c_int(num_experts), c_int(top),
+                                              c_int(group_count), c_int(group_keep), c_float(scale), c_float(eps),
+                                              _stream())
+    _check(st, "route_experts", f"{num_experts} experts (at most 1024), {top} chosen (at most 32)")
+    return ids, weights
+
+
+def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                   w_down: torch.Tensor, shared, logits, shared_gate_col: int, out_dtype) -> torch.Tensor:
+    """float32 [T, W]: sum_j weights[t, j] * down_e(silu(gate_e x_t) * up_e x_t) over the chosen experts
+    e = ids[t, j], in the order of j, plus (``shared`` [T, W], a tensor or split sums, given)
+    sigmoid(logits[t, shared_gate_col]) * shared[t].  ``w_gate_up`` [E, 2F, W] (an expert's gate rows,
+    then its up rows), ``w_down`` [E, W, F], both of x's type.  The (token, expert) pairs are sorted by
+    expert on the device into tiles of EXPERT_TILE_ROWS (or EXPERT_TILE_ROWS_LARGE) rows of one expert; a
+    row's sums run over k in an order that its tile does not change, so a token's result does not depend
+    on what else is in the step."""
+    _need(x, "x", None, 2)
+    _need(ids, "ids", torch.int32, 2)
+    _need(weights, "weights", torch.float32, 2)
+    _need(w_gate_up, "w_gate_up", x.dtype, 3)
+    _need(w_down, "w_down", x.dtype, 3)
+    t, w = x.shape
+    n_exp, two_f, w2 = w_gate_up.shape
+    f = two_f // 2
+    top = ids.shape[1]
+    if w2 != w or tuple(w_down.shape) != (n_exp, w, f) or two_f != 2 * f or tuple(weights.shape) != (t, top) \
+            or ids.shape[0] != t:
+        raise KernelError(f"routed_experts: x {tuple(x.shape)}, gate/up {tuple(w_gate_up.shape)}, down "
+                          f"{tuple(w_down.shape)}, ids {tuple(ids.shape)}")
+    lib = _lib("routed_experts")
+    dev = x.device
+    pairs = t * top
+    tile = EXPERT_TILE_ROWS_LARGE if pairs >= EXPERT_TILE_ROWS_LARGE * n_exp else EXPERT_TILE_ROWS
+    max_tiles = pairs // tile + min(n_exp, pairs) + 1
+    order = torch.empty(max_tiles * tile + max_tiles + n_exp + 2, dtype=torch.int32, device=dev)
+    st = lib.dib_moe_sort(_ptr(ids), c_int(pairs), c_int(n_exp), c_int(tile), c_int(max_tiles), _ptr(order), _stream())
+    _check(st, "routed_experts(sort)", f"{n_exp} experts (at most 1024)")
+    hidden = torch.empty(max_tiles * tile, f, dtype=x.dtype, device=dev)
+    st = lib.dib_moe_gate_up(_ptr(x), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), c_int(top),
+                             _ptr(w_gate_up), _ptr(hidden), c_int(f), c_int(w), _stream())
+    _check(st, "routed_experts(gate and up)")
+    per_pair = torch.empty(pairs, w, dtype=torch.float32, device=dev)
+    st = lib.dib_moe_down(_ptr(hidden), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), _ptr(w_down),
+                          _ptr(per_pair), c_int(f), c_int(w), _stream())
+    _check(st, "routed_experts(down)")
+    out = torch.empty(t, w, dtype=torch.float32, device=dev)
+    if shared is not None:
+        if tuple(shared.shape) != (t, w) or logits.shape[0] != t or logits.shape[1] <= shared_gate_col:
+            raise KernelError(f"routed_experts: shared output {tuple(shared.shape)}, logits {tuple(logits.shape)}")
+        sh, lg, row = _source_args(shared), _source_args(logits), logits.shape[1]
+    else:
+        sh = lg = (c_void_p(0), c_int(0), c_int(1), c_longlong(0))
+        row = 0
+    st = lib.dib_moe_combine(_ptr(per_pair), _ptr(weights), *sh, *lg, c_longlong(row), c_int(shared_gate_col),
+                             _ptr(out), c_int(t), c_int(top), c_int(w), _stream())
+    _check(st, "routed_experts(combine)")
+    return out
 
 
 # ---------------------------------------------------------------- softmax attention with a mask kind
@@ -1085,21 +1285,32 @@ def _cache_pages(kv_cache, page_elems: int, what: str) -> int:
 
 def attn_prepare(proj, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, q_norm_weight,
                  k_norm_weight, eps: float, freq, rotary_dim: int, positions: torch.Tensor, kv_cache,
-                 slot_mapping, page_size: int, out_dtype) -> torch.Tensor:
-    """From each token's projection row [q heads | k heads | v heads | anything else]: per-head RMS norm
-    of q and k (when a weight is given), rotation of the first ``rotary_dim`` elements of each head by
-    the token's position (element i with i + rotary_dim / 2, angle = position * freq[i], float32), q
-    [T, Hq, D] returned, k and v to the token's slot of the paged cache (a page: keys [Hkv, page_size,
-    D], then values [Hkv, page_size, Dv])."""
+                 slot_mapping, page_size: int, out_dtype, bias=None, norm_scope: str = "head",
+                 rotary_layout: str = "halves") -> torch.Tensor:
+    """From each token's projection row [q heads | k heads | v heads | anything else] (plus ``bias``,
+    float32 over q, k and v, when given): RMS norm of q and k (when a weight is given; ``norm_scope``
+    "head": per head, weights of head_dim elements; "projection": over all of q's (k's) heads at once,
+    weights of that many elements), rotation of the first ``rotary_dim`` elements of each head by the
+    token's position (``rotary_layout`` "halves": element i with i + rotary_dim / 2, "pairs": element 2i
+    with 2i + 1; angle = position * freq[i], float32), q [T, Hq, D] returned, k and v to the token's slot
+    of the paged cache (a page: keys [Hkv, page_size, D], then values [Hkv, page_size, Dv])."""
     t, width = proj.shape
     need = num_heads * head_dim + num_kv_heads * (head_dim + v_head_dim)
     if width < need:
         raise KernelError(f"attn_prepare: rows of {width} elements, q, k and v need {need}")
-    for w, n in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
+    if norm_scope not in ("head", "projection") or rotary_layout not in ("halves", "pairs"):
+        raise KernelError(f"attn_prepare: norm scope {norm_scope!r} or rotary layout {rotary_layout!r}")
+    whole = norm_scope == "projection"
+    for w, n, heads in ((q_norm_weight, "q_norm_weight", num_heads), (k_norm_weight, "k_norm_weight", num_kv_heads)):
         if w is not None:
             _need(w, n, torch.float32, 1)
-            if w.shape[0] != head_dim:
-                raise KernelError(f"{n} has {w.shape[0]} elements, heads have {head_dim}")
+            if w.shape[0] != (heads * head_dim if whole else head_dim):
+                raise KernelError(f"{n} has {w.shape[0]} elements for {heads} heads of {head_dim} "
+                                  f"(norm over the {norm_scope})")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != need:
+            raise KernelError(f"attn_prepare: a bias of {bias.shape[0]} elements, q, k and v have {need}")
     if freq is not None:
         _need(freq, "freq", torch.float32, 1)
         if freq.shape[0] * 2 != rotary_dim:
@@ -1111,6 +1322,16 @@ def attn_prepare(proj, num_heads: int, num_kv_heads: int, head_dim: int, v_head_
         _need(slot_mapping, "slot_mapping", torch.int32, 1)
         num_pages = _cache_pages(kv_cache, num_kv_heads * page_size * (head_dim + v_head_dim), "attn_prepare")
     q = torch.empty(t, num_heads, head_dim, dtype=out_dtype, device=proj.device)
+    if bias is not None or whole or rotary_layout == "pairs":
+        # a block per token: it sees all heads of the row at once
+        st = _lib("masked_attention").dib_attn_prepare_row(
+            *_source_args(proj), c_longlong(width), _ptr(bias), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight),
+            _ptr(k_norm_weight), c_int(1 if whole else 0), c_float(eps), _ptr(freq),
+            c_int(rotary_dim if freq is not None else 0), c_int(1 if rotary_layout == "pairs" else 0), _ptr(positions),
+            _ptr(slot_mapping), c_int(t), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
+            c_int(page_size), c_longlong(num_pages), c_int(_DT[out_dtype]), _stream())
+        _check(st, "attn_prepare(row)", f"heads {num_heads}/{num_kv_heads} of {head_dim}/{v_head_dim}")
+        return q
     st = _lib("masked_attention").dib_attn_prepare(
         *_source_args(proj), c_longlong(width), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight),
         c_float(eps), _ptr(freq), c_int(rotary_dim if freq is not None else 0), _ptr(positions),
@@ -1193,10 +1414,10 @@ HEADS_LINEAR_LIBRARY_ROWS = int(__import__("os").environ.get("DIB200_HEADS_LINEA
 
 def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, num_kv_heads: int,
                      v_head_dim: int, page_size: int, mask: str = "causal", mask_size=None, sink=None,
-                     gate=None, gate_col: int = 0, values_in_keys: bool = False) -> torch.Tensor:
+                     gate=None, gate_col: int = 0, values_in_keys: bool = False, keep_first: int = 0) -> torch.Tensor:
     """[T, Hq, Dv]: softmax attention of every token of the step over the keys of its sequence in the
     paged cache that ``mask`` lets it see (a query at position p: "causal" 0 .. p; "window" p - size + 1
-    .. p; "chunk" floor(p / size) * size .. p).  ``sink`` float32 [Hq]: the denominator also holds
+    .. p, and with ``keep_first`` also the keys 0 .. keep_first - 1; "chunk" floor(p / size) * size .. p).  ``sink`` float32 [Hq]: the denominator also holds
     exp(sink[h]) as one more term that brings nothing into the output and is taken as it is.  ``gate`` [T, >= gate_col + Hq * Dv] (a tensor or split
     sums): the output is multiplied by sigmoid(gate[t, gate_col + h * Dv + d]).  ``values_in_keys``: the
     cache holds keys only and a key's first Dv elements are its value."""
@@ -1208,6 +1429,9 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
         raise KernelError(f"masked_attention: {hq} heads over {num_kv_heads} key/value heads")
     _cache_pages(kv_cache, num_kv_heads * page_size * (dk + dv_stored), "masked_attention")
     kind, size = _mask_args(mask, mask_size)
+    keep = int(keep_first)
+    if keep < 0 or (keep and kind != 1):
+        raise KernelError("masked_attention: kept first keys belong to a window mask")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.shape[0] != hq:
@@ -1221,7 +1445,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
     _need(meta.token_seq, "token_seq", torch.int32, 1)
     _need(meta.positions, "positions", torch.int32, 1)
     out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
-    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and not values_in_keys and dk == v_head_dim \
+    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and not values_in_keys and dk == v_head_dim and not keep \
             and getattr(meta, "q_lens", None) is not None and getattr(meta, "num_decode", None) is not None:
         # keys and values of one size that the tensor-core kernels of ``attention_bf16`` take: the
         # split-KV decode kernels for the step's one-token sequences, the tcgen05 kernel (heads of
@@ -1266,7 +1490,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                 max_chunks = 1
                 if decoded:
                     # the most key tiles a decoded token can have
-                    most = (size // 64 + 2) if kind else (max(meta.kv_lens[:n_dec]) // 64 + 1)
+                    most = (size // 64 + 2 + -(-keep // 64)) if kind else (max(meta.kv_lens[:n_dec]) // 64 + 1)
                     max_chunks = -(-most // MASKED_DECODE_CHUNK_TILES)
                     if max_chunks > 1:
                         part_o = torch.empty(n_dec, hq, max_chunks, v_head_dim, dtype=torch.float32, device=q.device)
@@ -1276,8 +1500,8 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                     _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(meta.cu_q_lens), _ptr(tiles),
                     c_int(tiles.shape[0]), _ptr(sink),
                     c_int(hq), c_int(num_kv_heads), c_int(dk), c_int(v_head_dim), c_int(dv_stored),
-                    c_int(page_size), c_float(scale), c_int(kind), c_int(size), *gate_args, c_longlong(gate_row),
-                    c_longlong(gate_col), c_int(form_rows), _ptr(part_o), _ptr(part_ml),
+                    c_int(page_size), c_float(scale), c_int(kind), c_int(size), c_int(keep), *gate_args,
+                    c_longlong(gate_row), c_longlong(gate_col), c_int(form_rows), _ptr(part_o), _ptr(part_ml),
                     c_int(MASKED_DECODE_CHUNK_TILES), c_int(max_chunks), c_int(n_dec), _stream())
                 _check(st, "masked_attention(tensor cores)", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}",
                        kernels=2 if part_o is not None else 1)
@@ -1285,7 +1509,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
     st = _lib("masked_attention").dib_masked_attention(
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
         _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(num_kv_heads), c_int(dk),
-        c_int(v_head_dim), c_int(dv_stored), c_int(page_size), c_float(scale), c_int(kind), c_int(size),
+        c_int(v_head_dim), c_int(dv_stored), c_int(page_size), c_float(scale), c_int(kind), c_int(size), c_int(keep),
         _ptr(sink), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(_dt(q, "q")), _stream())
     _check(st, "masked_attention", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}")
     return out

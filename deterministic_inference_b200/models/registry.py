@@ -16,6 +16,7 @@ from pathlib import Path
 import torch
 
 from ..config.gamilorn_config import GamilornConfig
+from ..config.kipezen_config import KipezenConfig
 from ..config.model_config import Qwen3Config
 from ..config.zatirax_config import ZatiraxConfig
 from .decoder import DecoderModel
@@ -35,6 +36,7 @@ def register_architecture(name: str, config_class: type) -> None:
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Gamilorn", GamilornConfig)
 register_architecture("Zatirax", ZatiraxConfig)
+register_architecture("Kipezen", KipezenConfig)
 
 
 def config_from_dir(model_dir):

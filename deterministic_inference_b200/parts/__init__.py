@@ -7,5 +7,5 @@ from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, 
                        register_head, register_mixer, register_norm, register_position_encoding)
 from .spec import (CompositeSpec, LayerSpec, ModelPlan, PagedKVSpec, PartSpec, ScheduleEntry, StateSpec,
                    TensorSpec)
-from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, masked_attention, norm,
-               parallel, position, sigmoid_attention)  # noqa: F401  (register the kinds)
+from . import (attention, block, delta_rule, embedding, feed_forward, gated_delta_rule, gated_linear_recurrence,
+               latent_attention, masked_attention, norm, parallel, position, routed_experts, sigmoid_attention)  # noqa: F401  (register the kinds)

@@ -3,10 +3,12 @@
 ``pre_norm``: norm -> mixer -> norm -> feed-forward, the residual carried beside
 the hidden state: the first norm site takes the embedding as the residual, every
 later one adds the previous part's output to the residual and norms the sum
-(sid/model/qwen3.py:94-108)."""
+(sid/model/qwen3.py:94-108).  The float32-stream forms below keep the residual
+stream in float32 whatever type the parts compute in."""
 
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Block
 from .registry import NORMS, register_block
 from .spec import PartSpec
@@ -85,4 +87,30 @@ class SandwichStreamBlock(Block):
             return hidden, residual
         hidden, residual = self.feed_forward_norm.add_forward(hidden, residual)
         hidden = self.feed_forward_post_norm.forward(self.feed_forward.forward(hidden))
+        return hidden, residual
+
+
+@register_block("post_norm_f32_stream")
+class PostNormStreamBlock(Block):
+    """The norm sits on a sublayer's OUTPUT only, the residual stream is float32, and the sublayers
+    read the stream itself: x <- x + norm1(mixer(x)), then x <- x + norm2(feed_forward(x)).  The two
+    norms are ``stream_post_norm`` parts; what they return joins the stream inside the kernel that
+    hands the stream to the next sublayer (``ops.stream_read``: the sum stays float32, the copy the
+    sublayer reads is of the engine's type), so the block hands its last sublayer's normed output on
+    as the pending term.  A layer without a feed-forward (kind "none") hands on its mixer's."""
+
+    def __init__(self, ctx, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.dtype = ctx.dtype
+
+    def forward(self, hidden, residual, step, cache):
+        if residual is None:
+            residual, hidden = hidden, None
+        x = ops.stream_read(residual, hidden, self.dtype)
+        hidden = self.mixer_norm.forward(self.mixer.forward(x, step, cache))
+        if self.feed_forward.kind == "none":
+            return hidden, residual
+        x = ops.stream_read(residual, hidden, self.dtype)
+        hidden = self.feed_forward_norm.forward(self.feed_forward.forward(x))
         return hidden, residual

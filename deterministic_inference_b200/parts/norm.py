@@ -64,23 +64,27 @@ class StreamRMSNorm(Norm):
 @register_norm("stream_post_norm")
 class StreamPostNorm(Norm):
     """RMSNorm of a part's OUTPUT on its way into a float32 residual stream:
-    stream += x / sqrt(mean(x^2) + eps) * w.  ``forward`` only wraps its input (``ops.NormedTerm``);
-    the stream's next norm (or ``ops.stream_add_``) computes it in float32 and adds it unrounded."""
+    stream += x / sqrt(mean(x^2) + eps) * (weight_offset + w).  ``forward`` only wraps its input
+    (``ops.NormedTerm``); the stream's next reader (its next norm, ``ops.stream_read`` or
+    ``ops.stream_add_``) computes it in float32 and adds it unrounded.  ``weight_offset`` 1: the
+    weight is stored around zero."""
 
-    def __init__(self, ctx, name: str, size: int, eps: float):
+    def __init__(self, ctx, name: str, size: int, eps: float, weight_offset: float = 0.0):
         self.name, self.size, self.eps = name, int(size), float(eps)
+        self.weight_offset = float(weight_offset)
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.name, (self.size,), role="vector", init="one_plus_normal")]
+        return [TensorSpec(self.name, (self.size,), role="vector",
+                           init="normal" if self.weight_offset else "one_plus_normal")]
 
     def load(self, tensors):
-        self.weight = tensors[self.name]
+        w = tensors[self.name]
+        self.weight = (w + self.weight_offset).contiguous() if self.weight_offset else w
 
     def forward(self, x):
-        if isinstance(x, ops.SplitSum) or isinstance(x, torch.Tensor):
-            return ops.NormedTerm(x, self.weight, self.eps)
-        return ops.NormedTerm(ops.as_tensor(x), self.weight, self.eps)
+        # (a tensor, split sums, or a weighted sum of several mixers' outputs: the reader adds it up)
+        return ops.NormedTerm(x, self.weight, self.eps)
 
 
 @register_norm("none")

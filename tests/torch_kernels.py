@@ -322,8 +322,14 @@ def stream_add_(stream, term=None, bias=None, norm_weight=None, norm_eps=0.0, ou
     if bias is not None:
         stream += bias
     if out is not None:
-        out.copy_(_rms(stream, norm_weight, norm_eps).to(out.dtype))
+        out.copy_((stream if norm_weight is None else _rms(stream, norm_weight, norm_eps)).to(out.dtype))
     return stream
+
+
+def stream_read(stream, term, out_dtype):
+    if term is not None:
+        stream += _plain(term)
+    return stream if out_dtype == torch.float32 else stream.to(out_dtype)
 
 
 def limited_gate(gate_up, limit, alpha, out_dtype):
@@ -344,17 +350,37 @@ def _rotate_first(x, positions, freq, rot):
     return torch.cat([u * c - v * s, v * c + u * s, x[..., rot:]], dim=-1)
 
 
+def _rotate_pairs(x, positions, freq, rot):
+    """x [T, heads, D] float32: elements 2i and 2i + 1 (i < rot / 2) turned by position * freq[i]."""
+    if freq is None or rot == 0:
+        return x
+    a = positions[:x.shape[0]].float()[:, None] * freq[None, :]
+    c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+    u, v = x[..., 0:rot:2], x[..., 1:rot:2]
+    out = x.clone()
+    out[..., 0:rot:2] = u * c - v * s
+    out[..., 1:rot:2] = v * c + u * s
+    return out
+
+
 def attn_prepare(proj, num_heads, num_kv_heads, head_dim, v_head_dim, q_norm_weight, k_norm_weight, eps, freq,
-                 rotary_dim, positions, kv_cache, slot_mapping, page_size, out_dtype):
-    x = _plain(proj).to(out_dtype).float()
-    t = x.shape[0]
+                 rotary_dim, positions, kv_cache, slot_mapping, page_size, out_dtype, bias=None, norm_scope="head",
+                 rotary_layout="halves"):
+    t = proj.shape[0]
     nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_head_dim
-    q = x[:, :nq].reshape(t, num_heads, head_dim)
-    k = x[:, nq:nq + nk].reshape(t, num_kv_heads, head_dim)
-    v = x[:, nq + nk:nq + nk + nv].reshape(t, num_kv_heads, v_head_dim)
+    x = _plain(proj)[:, :nq + nk + nv]
+    if bias is not None:
+        x = x + bias
+    x = x.to(out_dtype).float()
+    q, k = x[:, :nq], x[:, nq:nq + nk]
+    if norm_scope == "head":
+        q, k = q.reshape(t, num_heads, head_dim), k.reshape(t, num_kv_heads, head_dim)
     if q_norm_weight is not None:
         q, k = _rms(q, q_norm_weight, eps), _rms(k, k_norm_weight, eps)
-    q, k = _rotate_first(q, positions, freq, rotary_dim), _rotate_first(k, positions, freq, rotary_dim)
+    q, k = q.reshape(t, num_heads, head_dim), k.reshape(t, num_kv_heads, head_dim)
+    v = x[:, nq + nk:nq + nk + nv].reshape(t, num_kv_heads, v_head_dim)
+    rotate = _rotate_pairs if rotary_layout == "pairs" else _rotate_first
+    q, k = rotate(q, positions, freq, rotary_dim), rotate(k, positions, freq, rotary_dim)
     if kv_cache is not None:
         flat = kv_cache.view(kv_cache.shape[0], -1)
         v_base = num_kv_heads * page_size * head_dim
@@ -394,7 +420,7 @@ def heads_linear(x, weight, out):
 
 
 def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_size, mask="causal", mask_size=None,
-                     sink=None, gate=None, gate_col=0, values_in_keys=False):
+                     sink=None, gate=None, gate_col=0, values_in_keys=False, keep_first=0):
     t, hq, dk = q.shape
     flat = kv_cache.view(kv_cache.shape[0], -1)
     keys_of = flat[:, :num_kv_heads * page_size * dk].view(-1, num_kv_heads, page_size, dk)
@@ -408,6 +434,8 @@ def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_si
         p = positions[i]
         lo = 0 if mask == "causal" else (max(0, p - mask_size + 1) if mask == "window" else p // mask_size * mask_size)
         js = torch.arange(lo, p + 1)
+        if keep_first and lo > 0:
+            js = torch.cat([torch.arange(0, min(keep_first, lo)), js])
         pages = meta.block_table[seqs[i]][js // page_size].long()
         for h in range(hq):
             k = keys_of[pages, h // group, js % page_size].float()
@@ -424,7 +452,119 @@ def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_si
     return out
 
 
-ALL = ("embedding_scaled", "stream_add_", "limited_gate", "attn_prepare", "latent_prepare", "heads_linear",
+# ---- gated delta rule with short convolutions, a gated linear recurrent unit, routed experts
+
+def _conv_with_tail(x, taps_w, tail, cu, slots, conv_bias=None):
+    """x [T, C] float32, taps_w [C, K], tail [slots, K - 1, C] (updated in place for slots != 0): per
+    sequence of the step the causal convolution over its tokens, the K - 1 inputs before them from the
+    tail."""
+    k = taps_w.shape[1]
+    out = torch.empty_like(x)
+    for b in range(len(slots)):
+        a, e = cu[b], cu[b + 1]
+        if e <= a:
+            continue
+        old = tail[slots[b]] if slots[b] else torch.zeros_like(tail[0])
+        seq = torch.cat([old, x[a:e]], dim=0)
+        y = torch.zeros(e - a, x.shape[1])
+        for j in range(k):
+            y = y + seq[j:j + e - a] * taps_w[:, j]
+        out[a:e] = y if conv_bias is None else y + conv_bias
+        if slots[b] and k > 1:
+            tail[slots[b]] = seq[-(k - 1):]
+    return out
+
+
+def gated_delta_rule(proj, conv_weight, a_log, dt_bias, norm_weight, state, step, num_heads, num_kv_heads,
+                     head_dim, v_head_dim, taps, key_eps, norm_eps, out_dtype):
+    x = _plain(proj)
+    t, h, g, d, e = x.shape[0], num_heads, num_kv_heads, head_dim, v_head_dim
+    chan = 2 * g * d + h * e
+    cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
+    n_state = h * d * e
+    tail = state[:, n_state:].view(state.shape[0], taps - 1, chan)
+    c = _conv_with_tail(x[:, :chan], conv_weight, tail, cu, slots)
+    c = c * torch.sigmoid(c)
+    q, k = c[:, :g * d].reshape(t, g, d), c[:, g * d:2 * g * d].reshape(t, g, d)
+    v = c[:, 2 * g * d:].reshape(t, h, e)
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + key_eps) * d ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + key_eps)
+    q, k = q.repeat_interleave(h // g, dim=1), k.repeat_interleave(h // g, dim=1)
+    gate = x[:, chan:chan + h * e].reshape(t, h, e)
+    beta = torch.sigmoid(x[:, chan + h * e:chan + h * e + h])
+    decay = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(x[:, chan + h * e + h:chan + h * e + 2 * h] + dt_bias))
+    o = torch.zeros(t, h, e)
+    for b in range(len(slots)):
+        s = state[slots[b], :n_state].view(h, d, e).clone() if slots[b] else torch.zeros(h, d, e)
+        for i in range(cu[b], cu[b + 1]):
+            s = s * decay[i][:, None, None]
+            u = beta[i][:, None] * (v[i] - torch.einsum("hde,hd->he", s, k[i]))
+            s = s + k[i][:, :, None] * u[:, None, :]
+            o[i] = torch.einsum("hde,hd->he", s, q[i])
+        if slots[b]:
+            state[slots[b], :n_state] = s.reshape(-1)
+    o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + norm_eps) * norm_weight
+    return (o * gate * torch.sigmoid(gate)).reshape(t, h * e).to(out_dtype)
+
+
+def gated_linear_recurrence(proj, bias, conv_weight, conv_bias, gates, gate_bias, neg_rate, state, step, width,
+                            blocks, taps, out_dtype):
+    x = _plain(proj) + bias
+    t, c = x.shape[0], width
+    cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
+    tail = state[:, c:].view(state.shape[0], taps - 1, c)
+    z = x[:, :c]
+    y = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    u = _conv_with_tail(x[:, c:], conv_weight, tail, cu, slots, conv_bias)
+    ub = u.view(t, blocks, c // blocks)
+    r = torch.sigmoid(torch.einsum("nbi,bio->nbo", ub, gates[0]).reshape(t, c) + gate_bias[0])
+    i = torch.sigmoid(torch.einsum("nbi,bio->nbo", ub, gates[1]).reshape(t, c) + gate_bias[1])
+    a = torch.exp(r * neg_rate)
+    xin = torch.sqrt(1.0 - a * a) * i * u
+    out = torch.empty(t, c)
+    for b in range(len(slots)):
+        s = state[slots[b], :c].clone() if slots[b] else torch.zeros(c)
+        for j in range(cu[b], cu[b + 1]):
+            s = a[j] * s + xin[j]
+            out[j] = s * y[j]
+        if slots[b]:
+            state[slots[b], :c] = s
+    return out.to(out_dtype)
+
+
+def route_experts(logits, correction, num_experts, top, group_count, group_keep, scale, eps):
+    z = _plain(logits)[:, :num_experts]
+    s = torch.sigmoid(z)
+    choice = s + correction
+    per = num_experts // group_count
+    by_group = choice.view(-1, group_count, per)
+    group_score = by_group.topk(min(2, per), dim=-1).values.sum(-1)
+    best = group_score.topk(group_keep, dim=-1).indices
+    allowed = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, best, True)
+    masked = by_group.masked_fill(~allowed[:, :, None], float("-inf")).reshape(-1, num_experts)
+    ids = masked.topk(top, dim=-1).indices
+    w = s.gather(1, ids)
+    w = w / (w.sum(-1, keepdim=True) + eps) * scale
+    return ids.to(torch.int32), w
+
+
+def routed_experts(x, ids, weights, w_gate_up, w_down, shared, logits, shared_gate_col, out_dtype):
+    t, w = x.shape
+    f = w_gate_up.shape[1] // 2
+    out = torch.zeros(t, w)
+    for i in range(t):
+        for j in range(ids.shape[1]):
+            e = int(ids[i, j])
+            gu = w_gate_up[e].float() @ x[i].float()
+            hdn = (gu[:f] * torch.sigmoid(gu[:f]) * gu[f:]).to(x.dtype).float()
+            out[i] += weights[i, j] * (w_down[e].float() @ hdn)
+    if shared is not None:
+        out = out + torch.sigmoid(_plain(logits)[:, shared_gate_col:shared_gate_col + 1]) * _plain(shared)
+    return out
+
+
+ALL = ("stream_read", "gated_delta_rule", "gated_linear_recurrence", "route_experts", "routed_experts",
+       "embedding_scaled", "stream_add_", "limited_gate", "attn_prepare", "latent_prepare", "heads_linear",
        "masked_attention", "embedding_positions", "stream_rms_norm", "xielu", "softcap_", "qkv_bias_cache", "sigmoid_attention",
        "delta_rule", "patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
        "paged_attention", "silu_mul", "gated_linear", "gather_rows", "linear", "argmax", "gumbel_sample")
