@@ -332,6 +332,38 @@ def zatirax_like(q, layers: int, chunk: int, window: int, rank: int, rot: int):
         "layers": [att, lat]})
 
 
+KIPEZEN_SIZES = {
+    # name -> the Kipezen sizes that go with the Qwen3 preset of DESIGN_SIZES[name]: the delta and the attention
+    # heads are Qwen3's, the recurrent unit is as wide as the model in blocks of 128 channels, and a token's
+    # experts (the chosen ones and the shared one) hold as many weights as Qwen3's dense feed-forward
+    "0_6b": dict(window=1024, keep=4, taps=4, experts=16, top=2, expert_ff=768, shared_ff=1536, groups=(4, 2)),
+    "8b": dict(window=4096, keep=4, taps=4, experts=32, top=4, expert_ff=1536, shared_ff=6144, groups=(8, 4)),
+}
+
+
+def kipezen_like(q, layers: int, window: int, keep: int, taps: int, experts: int, top: int, expert_ff: int,
+                 shared_ff: int, groups: tuple):
+    """A Kipezen configuration with the layer sizes of the Qwen3 configuration ``q``: delta layers and
+    parallel layers (attention beside the recurrent unit) in turn, every one with routed experts."""
+    from deterministic_inference_b200.config.kipezen_config import KipezenConfig
+    d = q.head_dim
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups[0], "keep": groups[1]}}}
+    delta = {"type": "delta", "mlp": mlp,
+             "mixer": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads, "dim": d, "vdim": d,
+                       "conv": taps}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads, "dim": d, "vdim": d,
+                              "scale": d ** -0.5, "mask": {"size": window, "keep_first": keep},
+                              "rot": {"base": 10000.0, "dims": d // 2}},
+                     "left_scale": 1.0,
+                     "right": {"width": q.hidden_size, "blocks": q.hidden_size // 128, "conv": taps},
+                     "right_scale": 1.0}}
+    return KipezenConfig.from_dict({
+        "architecture": "Kipezen", "vocab": q.vocab_size, "width": q.hidden_size, "max_positions": 8192,
+        "norm": {"eps": 1e-6}, "layers": [delta if i % 2 == 0 else par for i in range(layers)]})
+
+
 def design_arm(a) -> int:
     """``--design zatirax``: the same for the Zatirax design.  ``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
     real models (random weights, ``--design-layers`` layers), beside Qwen3 at the same sizes, and
@@ -592,22 +624,136 @@ def design_arm(a) -> int:
                     cache.release_slot(sl)
         return rows
 
+    def kipezen_kernel_rows(eng_k, eng_g, kcfg, gcfg):
+        """Kipezen's kernels and the like kernels of Gamilorn (the closest design: attention with a window
+        and kept first keys beside a delta rule, a float32 stream) on one layer's shapes: a prompt of
+        ``n_prompt`` tokens, and a decode step of 8 requests with ``ctx`` cached tokens."""
+        rows = {}
+        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        dl, par = kcfg.layers[0]["mixer"], kcfg.layers[1]["mixer"]
+        left, right, mlp = par["left"], par["right"], kcfg.layers[0]["mlp"]
+        hq, hkv, d, w = left["heads"], left["kv_heads"], left["dim"], kcfg.width
+        win, keep = left["mask"]["size"], left["mask"]["keep_first"]
+        n_exp, top, eff, sff = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"], mlp["shared"]["ff"]
+        g_right = gcfg.layers[0]["mixer"]["right"]
+        rh, rd, rank = g_right["heads"], g_right["dim"], g_right["decay_rank"]
+        g_ff = gcfg.layers[0]["mlp"]["ff"]
+        bf = torch.bfloat16
+
+        def row(name, ms, nbytes, flops):
+            floor = max(nbytes / hbm, flops / tf) * 1e3
+            rows[name] = {"ms": round(ms, 4), "roofline_ms": round(floor, 4), "of_roofline": round(floor / ms, 4)}
+
+        for what, batch, q_len, before in (("prompt", 1, n_prompt, 0), ("decode_b8", 8, 1, ctx)):
+            t = batch * q_len
+            span = range(before, before + q_len)
+            keys = batch * sum(min(p + 1, win + keep) for p in span)
+            held = min(before + q_len, win + keep)
+            att_bytes, att_flops = 2 * (2 * t * hq * d + batch * hkv * 2 * d * held), 4 * keys * hq * d
+            for eng, mine in ((eng_k, True), (eng_g, False)):
+                runner, cache = eng.runner, eng.cache
+                slots = [cache.allocate_slot() for _ in range(batch)]
+                if before:
+                    for sl in slots:
+                        runner.step([SequenceInput(sl, prompt_of(1000, before), 0, [])])
+                entries = [SequenceInput(sl, [1] * q_len, before, []) for sl in slots]
+                for e_ in entries:
+                    cache.allocate(e_.slot, before + q_len)
+                cache.reset_fresh_state()
+                step = build_step_batch(entries, cache, dev)
+                q = torch.randn(t, hq, d, device=dev).to(bf)
+                x = torch.randn(t, w, device=dev).to(bf)
+                stream = torch.randn(t, w, device=dev)
+                one_w = torch.ones(w, device=dev)
+                blocks = runner.model.blocks
+                if mine:
+                    dview, pview = cache.view(0, step), cache.view(1, step)
+                    kv, rstate = pview.members[0], pview.members[1].state
+                    delta, att, glr = blocks[0].mixer, blocks[1].mixer.branches[0], blocks[1].mixer.branches[1]
+                    ff = blocks[0].feed_forward
+                    row(f"{what}: attention, window + kept first keys", timed(lambda: ops.masked_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, hkv, d, kv.page_size, "window", win, keep_first=keep)),
+                        att_bytes, att_flops)
+                    proj = torch.randn(t, (hq + 2 * hkv) * d, device=dev)
+                    row(f"{what}: q/k/v bias + norm over the projection + pair rotation + cache write", timed(
+                        lambda: ops.attn_prepare(proj, hq, hkv, d, d, att.q_norm, att.k_norm, 1e-6, att.freq,
+                                                 att.rotary_dim, step.positions, kv.kv, kv.slot_mapping, kv.page_size, bf,
+                                                 bias=att.b_in, norm_scope="projection", rotary_layout="pairs")),
+                        proj.numel() * 6, 0)
+                    h, g, e = dl["heads"], dl["kv_heads"], dl["vdim"]
+                    dproj = torch.randn(t, delta.w_in.shape[0], device=dev)
+                    row(f"{what}: gated delta rule (convolutions, recurrence, output)", timed(lambda: ops.gated_delta_rule(
+                        dproj, delta.conv, delta.a_log, delta.dt_bias, delta.norm_weight, dview.state, step, h, g, d, e,
+                        dl["conv"], 1e-6, 1e-6, bf)),
+                        batch * h * d * e * 4 * 2 + t * (dproj.shape[1] * 4 + h * e * 2), 8 * t * h * d * e)
+                    c, per = right["width"], right["width"] // right["blocks"]
+                    rproj = torch.randn(t, 2 * c, device=dev)
+                    row(f"{what}: gated linear recurrence (convolution, gates, scan)", timed(
+                        lambda: ops.gated_linear_recurrence(rproj, glr.b_in, glr.conv, glr.conv_bias, glr.gates,
+                                                            glr.gate_bias, glr.neg_rate, rstate, step, c, right["blocks"],
+                                                            right["conv"], bf)),
+                        t * c * (8 + 2) + batch * right["conv"] * c * 8 + 2 * c * per * 4, 4 * t * c * per)
+                    row(f"{what}: post norm + add into the float32 stream + read", timed(lambda: ops.stream_read(
+                        stream, ops.NormedTerm(x, one_w, 1e-6), bf)), t * w * (4 + 4 + 2 + 2), 0)
+                    logits = torch.randn(t, ff.w_router.shape[0], device=dev)
+                    row(f"{what}: router", timed(lambda: ops.route_experts(
+                        logits, ff.correction, n_exp, top, ff.group_count, ff.group_keep, 2.5, 1e-20)),
+                        t * (logits.shape[1] * 4 + top * 8), 0)
+                    ids, wts = ops.route_experts(logits, ff.correction, n_exp, top, ff.group_count, ff.group_keep, 2.5, 1e-20)
+                    row(f"{what}: routed experts (sort, gate and up, down, sum)", timed(lambda: ops.routed_experts(
+                        x, ids, wts, ff.w_gate_up, ff.w_down, None, None, n_exp, bf)),
+                        min(n_exp, t * top) * 3 * eff * w * 2 + t * w * 6, 2 * t * top * 3 * eff * w)
+                    row(f"{what}: feed-forward (router, shared expert, routed experts)", timed(lambda: ff.forward(x)),
+                        (min(n_exp, t * top) * eff + sff) * 3 * w * 2 + t * w * 6, 2 * t * 3 * (top * eff + sff) * w)
+                else:
+                    view = cache.view(0, step)
+                    kv = view.members[0]
+                    pb = torch.zeros(hq, device=dev)
+                    row(f"{what}: gamilorn sigmoid attention (window + kept first keys)", timed(lambda: ops.sigmoid_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, pb, d, kv.page_size, win, keep)), att_bytes, att_flops)
+                    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev)
+                    bias = torch.zeros((hq + 2 * hkv) * d, device=dev)
+                    row(f"{what}: gamilorn q/k/v bias + cache write", timed(lambda: ops.qkv_bias_cache(
+                        qkv, bias, hq, hkv, d, d, kv.kv, kv.slot_mapping, kv.page_size, bf)), qkv.numel() * 6, 0)
+                    width = 5 * rh * rd + rank
+                    proj = torch.randn(t, width, device=dev)
+                    w2 = (torch.randn(rank, rh * rd, device=dev) * 0.1).to(bf)
+                    vec, one = torch.zeros(rh * rd, device=dev), torch.ones(rh * rd, device=dev)
+                    state = view.members[1].state
+                    row(f"{what}: gamilorn delta rule (prepare, recurrence, output)", timed(lambda: ops.delta_rule(
+                        proj, w2, vec, vec, one, state, step, rh, rd, rank, 0.6, 1e-6, 1e-6, bf)),
+                        batch * rh * rd * rd * 4 * 2 + t * (width * 4 + rh * rd * 2), 8 * t * rh * rd * rd)
+                    row(f"{what}: gamilorn add + norm of the float32 stream (two terms)", timed(lambda: ops.stream_rms_norm(
+                        stream, one_w, 1e-6, bf, add=ops.WeightedSum([(1.0, x), (1.0, x)]))), t * w * (4 + 4 + 2 + 2 + 2), 0)
+                    ff = blocks[0].feed_forward
+                    row(f"{what}: gamilorn dense feed-forward", timed(lambda: ff.forward(x)),
+                        3 * g_ff * w * 2 + t * w * 4, 2 * t * 3 * g_ff * w)
+                for sl in slots:
+                    cache.release_slot(sl)
+        return rows
+
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
     for name in [x for x in a.design_sizes.split(",") if x.strip()]:
         preset_name, extra = DESIGN_SIZES[name]
         qcfg = preset(preset_name, num_hidden_layers=n_layers, max_window_layers=n_layers)
+        beside, bcfg = "qwen3", qcfg
         if a.design == "zatirax":
             extra = ZATIRAX_SIZES[name]
             gcfg = zatirax_like(qcfg, n_layers, **extra)
+        elif a.design == "kipezen":
+            # beside Gamilorn, the closest design, at the same layer sizes
+            beside, bcfg = "gamilorn", gamilorn_like(qcfg, n_layers, **extra)
+            extra = KIPEZEN_SIZES[name]
+            gcfg = kipezen_like(qcfg, n_layers, **extra)
         else:
             gcfg = gamilorn_like(qcfg, n_layers, **extra)
         out = {"layers": n_layers, "width": qcfg.hidden_size, "heads": f"{qcfg.num_attention_heads}/{qcfg.num_key_value_heads} x {qcfg.head_dim}",
                "ff": qcfg.intermediate_size, a.design: dict(extra, parameters=gcfg.num_parameters()),
-               "qwen3_parameters": qcfg.num_parameters()}
+               f"{beside}_parameters": bcfg.num_parameters()}
         engines = {}
-        for label, mcfg in ((a.design, gcfg), ("qwen3", qcfg)):
+        for label, mcfg in ((a.design, gcfg), (beside, bcfg)):
             eng = engines[label] = engine_for(mcfg)
             ms = prefill_ms(eng, mcfg.vocab_size)
             r = {"prefill_ms": round(ms, 3), "prefill_tok_s": round(n_prompt / (ms / 1e3))}
@@ -616,14 +762,15 @@ def design_arm(a) -> int:
                 r[f"decode_b{b}_ms"] = round(dms, 4)
                 r[f"decode_b{b}_tok_s"] = round(b / (dms / 1e3))
             out[label + "_result"] = r
-        rows_of = zatirax_kernel_rows if a.design == "zatirax" else kernel_rows
-        out["kernels"] = rows_of(engines[a.design], engines["qwen3"], gcfg, qcfg)
+        rows_of = {"zatirax": zatirax_kernel_rows, "kipezen": kipezen_kernel_rows}.get(a.design, kernel_rows)
+        out["kernels"] = rows_of(engines[a.design], engines[beside], gcfg, bcfg)
         sizes[name] = out
         del engines
         import gc
         gc.collect()
         torch.cuda.empty_cache()
-    print(json.dumps({"metric": f"{a.design} beside qwen3 at equal layer sizes (bf16, 1 B200)", "impl": "ours",
+    beside = "gamilorn" if a.design == "kipezen" else "qwen3"
+    print(json.dumps({"metric": f"{a.design} beside {beside} at equal layer sizes (bf16, 1 B200)", "impl": "ours",
                       "dtype": "bf16", "data": "synthetic, random weights", "n_gpus": 1,
                       "prompt_tokens": n_prompt, "decode_context": ctx, "decode_steps": a.point_steps,
                       "warmup": a.warmup, "l2": "flushed before every timed kernel; steps hold more than L2",
@@ -657,8 +804,8 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); the numbers of such a run are not a result")
-    ap.add_argument("--design", default=None, choices=["gamilorn", "zatirax"],
-                    help="measure this design beside Qwen3 at equal layer sizes instead of the default "
+    ap.add_argument("--design", default=None, choices=["gamilorn", "zatirax", "kipezen"],
+                    help="measure this design beside Qwen3 (kipezen: beside Gamilorn) at equal layer sizes instead of the default "
                          "workload (prints a line of its own)")
     ap.add_argument("--design-sizes", default="0_6b,8b", help=f"of {sorted(DESIGN_SIZES)}")
     ap.add_argument("--design-layers", type=int, default=4)

@@ -50,7 +50,7 @@ def compare(model_dir, reqs, dtype, device, page, tail, what, probes=None):
     return cfg, w, exact, bounds
 
 
-def shows(cfg, w, req, exact, bound, rows, what, change_cfg=None, change_req=None, factor=30.0):
+def shows(cfg, w, req, exact, bound, rows, what, change_cfg=None, change_req=None, factor=10.0):
     """The plain implementation with the change applied moves the probed rows by ``factor`` tolerances."""
     cfg2, req2 = copy.deepcopy(cfg), list(req)
     if change_cfg is not None:
@@ -144,7 +144,7 @@ def delta_case(tmp, dtype, device, heads, kv_heads, dim, vdim, taps, page=16, n=
     def unmark(r):
         r[2] = 50
     shows(cfg, w, toks, exact[0], bounds[0], [n - 2, n - 1], "a write lost from the state", change_req=unmark,
-          factor=10.0)
+          factor=5.0)
 
 
 # ---- the gated linear recurrent unit ------------------------------------------------------------------
@@ -169,7 +169,7 @@ def recurrence_case(tmp, dtype, device, width, blocks, taps, page=16, n=130, see
     def unmark(r):
         r[0] = 50
     shows(cfg, w, toks, exact[0], bounds[0], [n - 1], "a first token lost from the state", change_req=unmark,
-          factor=10.0)
+          factor=5.0)
 
 
 # ---- routed experts -------------------------------------------------------------------------------------
@@ -193,13 +193,13 @@ def experts_case(tmp, dtype, device, experts, top, ff, groups, shared, correctio
     router = lambda c: c["layers"][0]["mlp"]["router"]
     if groups is not None and groups[1] < groups[0]:
         shows(cfg, w, reqs[0], exact[0], bounds[0], rows, "groups ignored",
-              change_cfg=lambda c: router(c).update(groups={"count": 1, "keep": 1}), factor=10.0)
+              change_cfg=lambda c: router(c).update(groups={"count": 1, "keep": 1}), factor=5.0)
     w0 = dict(w)
     w0["l0.mlp.correction"] = torch.zeros_like(w["l0.mlp.correction"])
     moved = row_errors(pk.forward(cfg, w0, reqs[0]), exact[0])
-    assert top == experts or float(moved.max()) > 10.0 * bounds[0], "the correction would not show"
+    assert top == experts or float(moved.max()) > 5.0 * bounds[0], "the correction would not show"
     if shared is not None:
         w1 = dict(w)
         w1["l0.mlp.shared.sg"] = torch.zeros_like(w["l0.mlp.shared.sg"])
         moved = row_errors(pk.forward(cfg, w1, reqs[0]), exact[0])
-        assert float(moved.max()) > 10.0 * bounds[0], "the shared expert's gate would not show"
+        assert float(moved.max()) > 5.0 * bounds[0], "the shared expert's gate would not show"

@@ -33,7 +33,7 @@ def model_dirs(tmp_path_factory):
     (2, 2, 16, 24, 32, 16, 16, 16),       # a window of two pages, kept keys of one; a full rotation
     (3, 1, 24, 24, 21, 0, 12, 8),         # no kept keys; sizes that are multiples of nothing
     (2, 1, 16, 16, 9, 30, 4, 8),          # kept keys reach beyond the window
-    (4, 2, 64, 64, 50, 20, 32, 16),       # heads of 64: the tensor-core kernels
+    (4, 2, 64, 64, 50, 19, 32, 16),       # heads of 64: the tensor-core kernels
     (8, 2, 128, 64, 33, 17, 64, 32),      # heads of 128, values half as wide, pages of 32
 ])
 def test_windowed_attention_alone(tmp_path, dtype, heads, kv_heads, dim, vdim, window, keep, rot, page):
@@ -65,7 +65,7 @@ def test_routed_experts_alone(tmp_path, dtype, experts, top, ff, groups, shared,
     km.experts_case(tmp_path, dtype, "cuda", experts, top, ff, groups, shared, correction)
 
 
-@pytest.mark.parametrize("experts, top, count, keep", [(16, 2, 2, 1), (12, 3, 4, 2), (8, 8, 1, 1), (6, 1, 6, 3),
+@pytest.mark.parametrize("experts, top, count, keep", [(16, 3, 2, 1), (12, 3, 4, 2), (8, 8, 1, 1), (6, 1, 6, 3),
                                                         (64, 6, 8, 3), (256, 8, 8, 4), (10, 4, 5, 5)])
 def test_the_router_alone(experts, top, count, keep):
     """The choice and the weights for many rows at once, corrections of both signs, against the plain
