@@ -205,29 +205,53 @@ def mixed(lens, live=3, tail=12, seed=0):
     return steps
 
 
-def replay(runner, reqs, steps):
+def replay(runner, reqs, steps, routes=None):
     """Runs the schedule (steps of (request, how many of its next tokens)) through the runner's step
     function; a request gets its slot at its first entry and gives slot and pages back with its last
-    token.  Returns the logits of every position, one tensor per request."""
+    token.  Returns the logits of every position, one tensor per request.  ``routes`` (a dict): it
+    receives routes[request][k] = the experts [tokens, top] that the k-th feed-forward with a router
+    chose for the request's tokens (what its bfloat16 rounding made of close calls)."""
     from deterministic_inference_b200.engine import SequenceInput
+    from deterministic_inference_b200.kernels import ops
 
     got = [None] * len(reqs)
     done, slots = {}, {}
-    for entries in steps:
-        ins = []
-        for i, n in entries:
-            if i not in slots:
-                slots[i], done[i] = runner.cache.allocate_slot(), 0
-            ins.append(SequenceInput(slots[i], reqs[i][done[i]:done[i] + n], done[i], list(range(n))))
-        logits, batch = runner.step(ins)
-        logits = logits.detach().double().cpu()
-        for j, (i, n) in enumerate(entries):
-            if got[i] is None:
-                got[i] = torch.full((len(reqs[i]), logits.shape[1]), float("nan"), dtype=torch.float64)
-            got[i][done[i]:done[i] + n] = logits[torch.as_tensor(batch.logit_rows[j], dtype=torch.long)]
-            done[i] += n
-            if done[i] == len(reqs[i]):
-                runner.cache.release_slot(slots.pop(i))
+    calls = []
+    real = ops.route_experts
+
+    def spy(*args, **kw):
+        ids, weights = real(*args, **kw)
+        calls.append(ids)
+        return ids, weights
+    if routes is not None:
+        ops.route_experts = spy
+    try:
+        for entries in steps:
+            ins = []
+            for i, n in entries:
+                if i not in slots:
+                    slots[i], done[i] = runner.cache.allocate_slot(), 0
+                ins.append(SequenceInput(slots[i], reqs[i][done[i]:done[i] + n], done[i], list(range(n))))
+            calls.clear()
+            logits, batch = runner.step(ins)
+            logits = logits.detach().double().cpu()
+            if routes is not None:
+                at = 0
+                for j in batch.order:               # the step's tokens lie in batch order
+                    i, n = entries[j]
+                    for k, ids in enumerate(calls):
+                        mine = routes.setdefault(i, {}).setdefault(k, torch.zeros(len(reqs[i]), ids.shape[1], dtype=torch.long))
+                        mine[done[i]:done[i] + n] = ids[at:at + n].long().cpu()
+                    at += n
+            for j, (i, n) in enumerate(entries):
+                if got[i] is None:
+                    got[i] = torch.full((len(reqs[i]), logits.shape[1]), float("nan"), dtype=torch.float64)
+                got[i][done[i]:done[i] + n] = logits[torch.as_tensor(batch.logit_rows[j], dtype=torch.long)]
+                done[i] += n
+                if done[i] == len(reqs[i]):
+                    runner.cache.release_slot(slots.pop(i))
+    finally:
+        ops.route_experts = real
     runner.cache.check_invariants()
     assert not slots, f"requests {sorted(slots)} were not finished by the schedule"
     return got

@@ -203,34 +203,62 @@ def parallel_mixer(h, positions, w, p, c, eps, rnd=_keep):
 
 # ---- the feed-forward: routed experts and a gated shared expert ----------------------------------
 
-def route(h, w, p, c):
-    """(chosen experts [n, top], their weights [n, top]).  Scores sigmoid(W_router h); the choice
-    adds the stored correction, the weights do not; only experts of the ``keep`` best groups
-    (a group's score: the sum of its two largest choice scores) can be chosen."""
+def route(h, w, p, c, forced=None):
+    """(chosen experts [n, top], their weights [n, top], gap [n]).  Scores sigmoid(W_router h); the
+    choice adds the stored correction, the weights do not; only experts of the ``keep`` best groups
+    (a group's score: the sum of its two largest choice scores) can be chosen.  ``forced`` [n, top]:
+    experts to take instead of the rule's own choice (what an engine chose under its rounding); ``gap``
+    then says by how much a choice score, or a group's score, would have to move for the rule to make
+    that choice (0 where it is the rule's own)."""
     r = c["router"]
     n_exp, top = r["experts"], r["top"]
     s = torch.sigmoid(h @ w[p + "router"].T)
     choice = s + w[p + "correction"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
-    per = n_exp // groups["count"]
-    by_group = choice.view(-1, groups["count"], per)
+    count, keep = groups["count"], groups["keep"]
+    per = n_exp // count
+    by_group = choice.view(-1, count, per)
     group_score = by_group.topk(min(2, per), dim=-1).values.sum(-1)
-    best = group_score.topk(groups["keep"], dim=-1).indices
+    best = group_score.topk(keep, dim=-1).indices
     allowed = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, best, True)
     masked = by_group.masked_fill(~allowed[:, :, None], float("-inf")).reshape(-1, n_exp)
     chosen = masked.topk(top, dim=-1).indices
+    gap = torch.zeros(h.shape[0], dtype=choice.dtype)
+    if forced is not None:
+        forced = torch.as_tensor(forced, dtype=torch.long)
+        for t in range(h.shape[0]):
+            ids = forced[t].tolist()
+            if sorted(ids) == sorted(chosen[t].tolist()):
+                continue
+            if len(set(ids)) != top:
+                gap[t] = float("inf")
+                continue
+            # its groups must be among the best up to the gap ...
+            mine = sorted({e // per for e in ids})
+            kth = group_score[t].topk(keep).values[-1]
+            g_gap = max(float(kth - group_score[t, g]) for g in mine)
+            # ... and, within its groups filled up with the best others, its experts the best up to the gap
+            rest = [g for g in group_score[t].argsort(descending=True).tolist() if g not in mine]
+            mine = mine + rest[:max(keep - len(mine), 0)]
+            inside = torch.cat([by_group[t, g] for g in mine])
+            e_gap = float(inside.topk(top).values[-1] - choice[t, ids].min())
+            gap[t] = float("inf") if len(mine) > keep else max(g_gap, e_gap, 0.0)
+        chosen = forced
     weights = s.gather(1, chosen)
     weights = weights / (weights.sum(-1, keepdim=True) + 1e-20) * r["scale"]
-    return chosen, weights
+    return chosen, weights, gap
 
 
 def expert(h, w, p, rnd=_keep):
     return rnd(rnd(silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T)
 
 
-def moe_feed_forward(h, w, p, c, rnd=_keep, route_input=None):
-    """``route_input``: what the router reads (the unrounded h when h itself is a rounding)."""
-    chosen, weights = route(h if route_input is None else route_input, w, p, c)
+def moe_feed_forward(h, w, p, c, rnd=_keep, route_input=None, forced=None, gaps=None):
+    """``route_input``: what the router reads (the unrounded h when h itself is a rounding).  ``forced``,
+    ``gaps``: see ``route``; the tokens' gaps are appended to the list ``gaps``."""
+    chosen, weights, gap = route(h if route_input is None else route_input, w, p, c, forced)
+    if gaps is not None:
+        gaps.append(gap)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, a in zip(chosen[t].tolist(), weights[t]):
@@ -242,8 +270,10 @@ def moe_feed_forward(h, w, p, c, rnd=_keep, route_input=None):
 
 # ---- the model ----------------------------------------------------------------------------------------
 
-def forward(cfg, w, tokens, bf16_storage=False, return_layers=False):
-    """Logits [n, vocab] of one whole sequence."""
+def forward(cfg, w, tokens, bf16_storage=False, return_layers=False, forced=None, gaps=None):
+    """Logits [n, vocab] of one whole sequence.  ``forced`` {layer: [n, top]}: the experts to take in
+    that layer's feed-forward; ``gaps``: a list that receives, per such layer, how far each token's
+    forced choice is from the rule's own (see ``route``)."""
     rnd = as_stored_bf16 if bf16_storage else _keep
     eps = cfg["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -261,7 +291,8 @@ def forward(cfg, w, tokens, bf16_storage=False, return_layers=False):
             raise ValueError(layer["type"])
         x = x + one_plus_norm(m, w[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + one_plus_norm(moe_feed_forward(rnd(x), w, p + "mlp.", layer["mlp"], rnd, route_input=x),
+            x = x + one_plus_norm(moe_feed_forward(rnd(x), w, p + "mlp.", layer["mlp"], rnd, route_input=x,
+                                                   forced=None if forced is None else forced.get(i), gaps=gaps),
                                   w[p + "norm2"], eps)
         layers_out.append(x)
     logits = rnd(one_plus_norm(x, w["final.norm"], eps)) @ w["embed"].T
