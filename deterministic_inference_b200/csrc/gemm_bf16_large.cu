@@ -408,7 +408,10 @@ template <typename OutT, bool GATED, int BNL, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles,
-                  const __grid_constant__ QkvEpilogue qk) {
+                  const __grid_constant__ QkvEpilogue qk, const int* __restrict__ tile_matrix, int matrix_rows) {
+  // GROUPED (tile_matrix not null): the weights are a stack of matrices of matrix_rows rows each, and
+  // the token tile m multiplies matrix tile_matrix[m] (a negative entry: matrix 0, for a tile of
+  // padding whose result nobody reads).  The table is written by the kernel before this one.
   // (gated: a tile holds BNL / 2 gate rows and the BNL / 2 up rows of the same features)
   using TL = Tile<BNL, QKV>;
   constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
@@ -468,7 +471,11 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int total = my_tiles * num_kb;
         auto load_w = [&](int c) {
           const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
-          const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+          int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+          if (tile_matrix != nullptr) {
+            const int which = tile_matrix[t % m_tiles];
+            n0 += (which > 0 ? which : 0) * matrix_rows;
+          }
           unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
           tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
           if (BNL == 256 || GATED)     // (the weight map's boxes are 128 rows, or BNL / 2 for a gated tile)
@@ -479,6 +486,7 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           tma_load_2d(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK, (t % m_tiles) * BM, &full[c % STAGES]);
         };
         const int pre = total < STAGES ? total : STAGES;
+        if (tile_matrix != nullptr) pdl_wait();      // which matrix a tile takes is not known before
         for (int c = 0; c < pre; ++c) {
           mbar_expect_tx(&full[c], STAGE_BYTES);
           load_w(c);
@@ -836,9 +844,11 @@ bool make_out_map(CUtensorMap* map, void* ptr, long long M, long long N) {
 // (QKV: `out` is the q rows [M, out_cols]; the k and v rows go where `qk` says)
 template <typename OutT, bool GATED, int BNL, bool QKV = false>
 int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
-                 cudaStream_t st, const QkvEpilogue& qk = QkvEpilogue{}) {
+                 cudaStream_t st, const QkvEpilogue& qk = QkvEpilogue{}, const int* tile_matrix = nullptr,
+                 int matrices = 1) {
   CUtensorMap mx, mw, mo;
-  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, GATED ? BNL / 2 : 128) ||
+  const long long matrix_rows = GATED ? 2ll * N : (long long)N;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, matrices * matrix_rows, K, GATED ? BNL / 2 : 128) ||
       !make_out_map<OutT>(&mo, out, M, QKV ? (long long)qk.Hq * 128 : (long long)N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + BM - 1) / BM;
@@ -855,7 +865,8 @@ int launch_large(const void* x, const void* w, void* out, int M, int N, int K, i
     attr_set.mark();
   }
   const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, mo, M, N, K, m_tiles, n_tiles, qk);
+  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, mo, M, N, K, m_tiles, n_tiles, qk, tile_matrix,
+             (int)matrix_rows);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -967,6 +978,24 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
   if (shape == 2) return launch_pair<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
   if (shape == 0) return launch_large<__nv_bfloat16, true, 128>(x, w, out, M, I, K, sm_count, st);
   return launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
+}
+
+// A product per tile of 128 rows with one of a stack of matrices: row tile m of x [M, K] (M a multiple
+// of 128) times matrix tile_matrix[m] of w.  gated = 0: w [matrices, N, K], out [M, N] bfloat16 or
+// float32 (N a multiple of 256).  gated = 1: w [matrices, 2N, K] (gate rows, then up rows), out [M, N]
+// bfloat16 = silu(gate) * up (N a multiple of 128).  The table lies on the device and may be written
+// by the kernel before this one.  Tiles of 128 x 256 by one CTA.
+int dib_gemm_bf16_large_grouped(const void* x, const void* w, void* out, int M, int N, int K, int gated, int out_fp32,
+                                const int* tile_matrix, int matrices, int sm_count, cudaStream_t st) {
+  if (M == 0 || N == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0 || sm_count < 1 || M % BM != 0 || matrices < 1 || tile_matrix == nullptr ||
+      N % (gated ? 128 : 256) != 0 || (gated && out_fp32))
+    return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+    return DIB_BAD_ALIGN;
+  if (gated) return launch_large<__nv_bfloat16, true, 256>(x, w, out, M, N, K, sm_count, st, QkvEpilogue{}, tile_matrix, matrices);
+  if (out_fp32) return launch_large<float, false, 256>(x, w, out, M, N, K, sm_count, st, QkvEpilogue{}, tile_matrix, matrices);
+  return launch_large<__nv_bfloat16, false, 256>(x, w, out, M, N, K, sm_count, st, QkvEpilogue{}, tile_matrix, matrices);
 }
 
 // The fused q/k/v projection of a prompt portion: x [M, K] times w [(Hq + 2 Hkv) * 128, K]^T,

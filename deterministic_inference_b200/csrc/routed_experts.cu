@@ -351,8 +351,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ per_pair, const flo
 template <int MT, int NJ>
 int launch_product_mma(const void* a_rows, const int* order, int max_tiles, int tile, int top, const void* w, void* out,
                        int K, int N, int mode, cudaStream_t st) {
-  // the A rows' k are staged in runs of KC (a multiple of 64) that fit 64 KB
-  int KC = (64 * 1024 / (MT * 16 * 2) - GP_PAD) / 64 * 64;
+  // the A rows' k are staged in runs of KC (a multiple of 64) that fit 64 KB; tiles of 16 rows (decoded
+  // tokens: the product is bound by how many weight loads an SM keeps in flight) in runs that fit 16 KB,
+  // so that an SM holds many CTAs.  The runs do not change the order of a sum.
+  int KC = ((MT == 1 ? 16 : 64) * 1024 / (MT * 16 * 2) - GP_PAD) / 64 * 64;
   if (KC > (K + 63) / 64 * 64) KC = (K + 63) / 64 * 64;
   const size_t smem = (size_t)MT * 16 * (KC + GP_PAD) * 2;
   static DeviceOnce once;
@@ -390,9 +392,60 @@ int moe_product(const void* a_rows, int dtype, const int* order, int max_tiles, 
   return DIB_OK;
 }
 
+// ---- the sorted rows as matrices of their own (for the tensor-core product of whole tiles) ----------
+// a_sorted[row] = x[order[row] / top] (a padding row: zeros); 16 bytes a thread and step.
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ order, long long rows,
+                                       int top, int vecs, uint4* __restrict__ a_sorted) {
+  pdl_prologue(order);
+  const long long n = rows * vecs;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / vecs;
+    const int v = (int)(i - row * vecs);
+    const int pair = order[row];
+    a_sorted[i] = pair >= 0 ? x[(long long)(pair / top) * vecs + v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+// per_pair[order[row]] = y_sorted[row]
+__global__ void moe_scatter_rows_kernel(const float4* __restrict__ y_sorted, const int* __restrict__ order, long long rows,
+                                        int vecs, float4* __restrict__ per_pair) {
+  pdl_prologue(y_sorted);
+  const long long n = rows * vecs;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / vecs;
+    const int pair = order[row];
+    if (pair >= 0) per_pair[(long long)pair * vecs + (i - row * vecs)] = y_sorted[i];
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+// x bfloat16 [T, W] (W a multiple of 8) -> a_sorted bfloat16 [rows, W] in the order of `order`
+int dib_moe_gather_rows(const void* x, const int* order, long long rows, int top, int W, void* a_sorted,
+                        cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (W < 8 || W % 8 != 0 || top < 1) return DIB_BAD_SIZE;
+  const long long n = rows * (W / 8);
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  dib_launch(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, st, (const uint4*)x, order, rows, top, W / 8,
+             (uint4*)a_sorted);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// y_sorted float32 [rows, W] (W a multiple of 4) -> per_pair float32 [pairs, W]
+int dib_moe_scatter_rows(const float* y_sorted, const int* order, long long rows, int W, float* per_pair,
+                         cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (W < 4 || W % 4 != 0) return DIB_BAD_SIZE;
+  const long long n = rows * (W / 4);
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  dib_launch(moe_scatter_rows_kernel, dim3(blocks), dim3(256), 0, st, (const float4*)y_sorted, order, rows, W / 4,
+             (float4*)per_pair);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
 
 int dib_moe_route(const void* logits, int kind, int splits, long long stride, long long row_width,
                   const float* correction, int* ids, float* weights, int T, int E, int top, int groups, int keep,

@@ -1171,6 +1171,11 @@ def gated_linear_recurrence(proj, bias: torch.Tensor, conv_weight: torch.Tensor,
 # A row's bits do not depend on the tile it is computed in.
 EXPERT_TILE_ROWS = 16
 EXPERT_TILE_ROWS_LARGE = 64
+# bfloat16 steps that bring an expert EXPERT_TILE_ROWS_TC rows on average: the sorted rows become a
+# matrix of their own and both products run on the tcgen05 kernel of ``gemm_bf16_large`` (a tile of 128
+# rows times its expert's matrix).  DIB200_EXPERTS_TC=0 (read once) leaves that form out.
+EXPERT_TILE_ROWS_TC = 128
+EXPERTS_TC = __import__("os").environ.get("DIB200_EXPERTS_TC", "1") != "0"
 
 
 def route_experts(logits, correction: torch.Tensor, num_experts: int, top: int, group_count: int,
@@ -1222,19 +1227,44 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
     lib = _lib("routed_experts")
     dev = x.device
     pairs = t * top
-    tile = EXPERT_TILE_ROWS_LARGE if pairs >= EXPERT_TILE_ROWS_LARGE * n_exp else EXPERT_TILE_ROWS
+    on_tc = EXPERTS_TC and x.dtype == torch.bfloat16 and pairs >= EXPERT_TILE_ROWS_TC * n_exp \
+        and f % 128 == 0 and w % 256 == 0 and x.is_contiguous()
+    tile = EXPERT_TILE_ROWS_TC if on_tc \
+        else EXPERT_TILE_ROWS_LARGE if pairs >= EXPERT_TILE_ROWS_LARGE * n_exp else EXPERT_TILE_ROWS
     max_tiles = pairs // tile + min(n_exp, pairs) + 1
     order = torch.empty(max_tiles * tile + max_tiles + n_exp + 2, dtype=torch.int32, device=dev)
     st = lib.dib_moe_sort(_ptr(ids), c_int(pairs), c_int(n_exp), c_int(tile), c_int(max_tiles), _ptr(order), _stream())
     _check(st, "routed_experts(sort)", f"{n_exp} experts (at most 1024)")
-    hidden = torch.empty(max_tiles * tile, f, dtype=x.dtype, device=dev)
-    st = lib.dib_moe_gate_up(_ptr(x), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), c_int(top),
-                             _ptr(w_gate_up), _ptr(hidden), c_int(f), c_int(w), _stream())
-    _check(st, "routed_experts(gate and up)")
     per_pair = torch.empty(pairs, w, dtype=torch.float32, device=dev)
-    st = lib.dib_moe_down(_ptr(hidden), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), _ptr(w_down),
-                          _ptr(per_pair), c_int(f), c_int(w), _stream())
-    _check(st, "routed_experts(down)")
+    if on_tc:
+        from .gemm_bf16 import _sms
+        large = _lib("gemm_bf16_large")
+        rows = max_tiles * tile
+        tile_expert = c_void_p(order.data_ptr() + 4 * rows)
+        sorted_x = torch.empty(rows, w, dtype=x.dtype, device=dev)
+        st = lib.dib_moe_gather_rows(_ptr(x), _ptr(order), c_longlong(rows), c_int(top), c_int(w), _ptr(sorted_x),
+                                     _stream())
+        _check(st, "routed_experts(rows in the experts' order)")
+        hidden = torch.empty(rows, f, dtype=x.dtype, device=dev)
+        st = large.dib_gemm_bf16_large_grouped(_ptr(sorted_x), _ptr(w_gate_up), _ptr(hidden), c_int(rows), c_int(f),
+                                               c_int(w), c_int(1), c_int(0), tile_expert, c_int(n_exp),
+                                               c_int(_sms(dev)), _stream())
+        _check(st, "routed_experts(gate and up, tcgen05)", f"rows {rows}, F {f}, W {w}")
+        sorted_y = torch.empty(rows, w, dtype=torch.float32, device=dev)
+        st = large.dib_gemm_bf16_large_grouped(_ptr(hidden), _ptr(w_down), _ptr(sorted_y), c_int(rows), c_int(w),
+                                               c_int(f), c_int(0), c_int(1), tile_expert, c_int(n_exp),
+                                               c_int(_sms(dev)), _stream())
+        _check(st, "routed_experts(down, tcgen05)", f"rows {rows}, F {f}, W {w}")
+        st = lib.dib_moe_scatter_rows(_ptr(sorted_y), _ptr(order), c_longlong(rows), c_int(w), _ptr(per_pair), _stream())
+        _check(st, "routed_experts(rows back to their pairs)")
+    else:
+        hidden = torch.empty(max_tiles * tile, f, dtype=x.dtype, device=dev)
+        st = lib.dib_moe_gate_up(_ptr(x), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), c_int(top),
+                                 _ptr(w_gate_up), _ptr(hidden), c_int(f), c_int(w), _stream())
+        _check(st, "routed_experts(gate and up)")
+        st = lib.dib_moe_down(_ptr(hidden), c_int(_dt(x, "x")), _ptr(order), c_int(max_tiles), c_int(tile), _ptr(w_down),
+                              _ptr(per_pair), c_int(f), c_int(w), _stream())
+        _check(st, "routed_experts(down)")
     out = torch.empty(t, w, dtype=torch.float32, device=dev)
     if shared is not None:
         if tuple(shared.shape) != (t, w) or logits.shape[0] != t or logits.shape[1] <= shared_gate_col:

@@ -41,8 +41,10 @@ def compare(model_dir, reqs, dtype, device, page, tail, what, **engine):
     moe_layers = [i for i, layer in enumerate(cfg["layers"]) if layer.get("mlp") is not None]
     lens = [len(r) for r in reqs]
     for name, steps in ku.schedules(lens, tail).items():
-        runner = ku.runner_for(model_dir, dtype, device, page, lens, **engine)
         routes = {} if dtype == "bfloat16" and moe_layers else None
+        if routes is not None:
+            engine = dict(engine, cuda_graphs=False)      # a replayed graph does not show its router's choices
+        runner = ku.runner_for(model_dir, dtype, device, page, lens, **engine)
         got = ku.replay(runner, reqs, steps, routes)
         for i, (g, r) in enumerate(zip(got, reqs)):
             if dtype == "float32":
