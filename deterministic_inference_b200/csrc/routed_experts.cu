@@ -221,7 +221,8 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ a_rows, const int* __re
       *reinterpret_cast<uint4*>(As + r * as + c8 * 8) = v;
     }
     __syncthreads();
-#pragma unroll 2
+    // (tiles of 16 rows are bound by the weight loads in flight: four steps' loads are issued ahead)
+#pragma unroll(MT == 1 ? 4 : 2)
     for (int k = 0; k < kpad; k += 32) {
       uint4 b[NJ];
       const bool kin = k + tig * 8 < klen;
