@@ -74,6 +74,13 @@ CONFIGS = {
                    parallel(6, 1, 32, 16, 30, 40, 8, 100.0, 96, 1, 2, scales=(0.5, 1.5),
                             mlp=moe(10, 3, 48, 1.5, groups=(5, 3), shared=64)),
                    delta(4, 4, 16, 16, 2, mlp=None)]}),
+    # a width that is a multiple of 4 only, five heads, groups of ONE expert (a group's score is that
+    # expert's), a window shorter than a page, state sizes that are multiples of nothing
+    "k5": dict(page_size=16, seed=55, config={
+        "architecture": "Kipezen", "vocab": 131, "width": 100, "norm": {"eps": 1e-5},
+        "layers": [delta(5, 5, 12, 20, 3, mlp=moe(6, 2, 36, 1.0, groups=(6, 3), shared=20)),
+                   parallel(5, 5, 12, 20, 7, 2, 6, 3000.0, 50, 5, 2, scales=(1.1, 0.9),
+                            mlp=moe(9, 4, 28, 1.5, groups=(3, 2), shared=None))]}),
 }
 
 

@@ -129,6 +129,7 @@ CASES = {       # configuration -> request lengths, seed
     "k2": ([5, 33, 64, 200], 32),
     "k3": ([3, 22, 57, 130, 333], 33),
     "k4": ([1, 9, 40, 150, 300], 34),
+    "k5": ([2, 30, 75, 180], 36),
 }
 
 
