@@ -81,6 +81,13 @@ CONFIGS = {
         "layers": [delta(5, 5, 12, 20, 3, mlp=moe(6, 2, 36, 1.0, groups=(6, 3), shared=20)),
                    parallel(5, 5, 12, 20, 7, 2, 6, 3000.0, 50, 5, 2, scales=(1.1, 0.9),
                             mlp=moe(9, 4, 28, 1.5, groups=(3, 2), shared=None))]}),
+    # few wide experts: a prompt of some hundred tokens brings each of them 128 rows or more, so a
+    # bfloat16 engine runs their products on the tensor-core kernel of the dense layers
+    "k6": dict(page_size=16, seed=56, config={
+        "architecture": "Kipezen", "vocab": 160, "width": 256, "norm": {"eps": 1e-5},
+        "layers": [parallel(2, 1, 32, 32, 50, 3, 16, 10000.0, 64, 2, 2,
+                            mlp=moe(4, 2, 128, 2.0, groups=(2, 2), shared=128)),
+                   delta(2, 1, 32, 32, 3, mlp=moe(3, 1, 256, 1.5, shared=None))]}),
 }
 
 
