@@ -365,7 +365,8 @@ def kipezen_like(q, layers: int, window: int, keep: int, taps: int, experts: int
 
 
 def design_arm(a) -> int:
-    """``--design zatirax``: the same for the Zatirax design.  ``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
+    """``--design zatirax``: the same for the Zatirax design; ``--design kipezen``: for the Kipezen design,
+    beside Gamilorn (the closest design) instead of Qwen3.  ``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
     real models (random weights, ``--design-layers`` layers), beside Qwen3 at the same sizes, and
     the new design's kernels one by one beside the like kernels of Qwen3, each with its share of
     the measured roofline.  Prints one JSON line of its own; the default benchmark is untouched."""
