@@ -407,11 +407,13 @@ __device__ __forceinline__ void stores_done(int lane) {
 template <typename OutT, bool GATED, int BNL, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                  const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles,
+                  const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles_given, int n_tiles,
                   const __grid_constant__ QkvEpilogue qk, const int* __restrict__ tile_matrix, int matrix_rows) {
   // GROUPED (tile_matrix not null): the weights are a stack of matrices of matrix_rows rows each, and
   // the token tile m multiplies matrix tile_matrix[m] (a negative entry: matrix 0, for a tile of
-  // padding whose result nobody reads).  The table is written by the kernel before this one.
+  // padding whose result nobody reads).  The table is written by the kernel before this one, and the
+  // entry behind its m_tiles_given entries says how many token tiles are in use (they come first): the
+  // tiles of padding behind them are not computed.  Every role reads the count after the dependency wait.
   // (gated: a tile holds BNL / 2 gate rows and the BNL / 2 up rows of the same features)
   using TL = Tile<BNL, QKV>;
   constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
@@ -433,6 +435,12 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
+  int m_tiles = m_tiles_given;
+  if (tile_matrix != nullptr) {
+    pdl_wait();
+    const int used = tile_matrix[m_tiles_given];
+    m_tiles = used < 0 ? 0 : (used < m_tiles_given ? used : m_tiles_given);
+  }
   const int tiles = m_tiles * n_tiles;
   // tile t: token tile t % m_tiles of feature tile t / m_tiles; this CTA takes
   // blockIdx.x, blockIdx.x + gridDim.x, ...
@@ -984,7 +992,8 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
 // of 128) times matrix tile_matrix[m] of w.  gated = 0: w [matrices, N, K], out [M, N] bfloat16 or
 // float32 (N a multiple of 256).  gated = 1: w [matrices, 2N, K] (gate rows, then up rows), out [M, N]
 // bfloat16 = silu(gate) * up (N a multiple of 128).  The table lies on the device and may be written
-// by the kernel before this one.  Tiles of 128 x 256 by one CTA.
+// by the kernel before this one; it has M / 128 entries and one more, the number of row tiles in use
+// (the first ones; the rows of the others are left as they are).  Tiles of 128 x 256 by one CTA.
 int dib_gemm_bf16_large_grouped(const void* x, const void* w, void* out, int M, int N, int K, int gated, int out_fp32,
                                 const int* tile_matrix, int matrices, int sm_count, cudaStream_t st) {
   if (M == 0 || N == 0) return DIB_OK;

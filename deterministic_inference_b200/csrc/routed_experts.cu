@@ -106,7 +106,8 @@ moe_route_kernel(Source logits, long long row_width, const float* __restrict__ c
 }
 
 // ---- the sort -----------------------------------------------------------------------------------
-// order: int32 [max_tiles * tile] row -> pair (-1: padding), then [max_tiles] tile -> expert (-1: unused).
+// order: int32 [max_tiles * tile] row -> pair (-1: padding), then [max_tiles] tile -> expert (-1: unused), then
+// one entry: the number of tiles in use (they are the first ones).
 // One block.  Where a pair lands inside its expert's rows depends on the order in which threads arrive,
 // which no result depends on (a row's sums do not know the row's place).
 constexpr int SORT_THREADS = 1024;
@@ -141,6 +142,7 @@ moe_sort_kernel(const int* __restrict__ ids, int pairs, int E, int tile, int max
   __syncthreads();
   if (e < E)
     for (int k = first_tile[e]; k < first_tile[e + 1] && k < max_tiles; ++k) tile_expert[k] = e;
+  if (e == 0) tile_expert[max_tiles] = first_tile[E] < max_tiles ? first_tile[E] : max_tiles;   // tiles in use: the first ones
   for (int i = threadIdx.x; i < pairs; i += SORT_THREADS) {
     const int x = ids[i];
     if (x < 0 || x >= E) continue;
@@ -463,7 +465,7 @@ int dib_moe_route(const void* logits, int kind, int splits, long long stride, lo
   return DIB_OK;
 }
 
-// order: int32 [max_tiles * tile + max_tiles]; max_tiles >= pairs / tile + min(E, pairs)
+// order: int32 [max_tiles * tile + max_tiles + 1]; max_tiles >= pairs / tile + min(E, pairs)
 int dib_moe_sort(const int* ids, int pairs, int E, int tile, int max_tiles, int* order, cudaStream_t st) {
   if (pairs == 0) return DIB_OK;
   if (E < 1 || E > SORT_THREADS || tile < 1 || max_tiles < 1) return DIB_BAD_SIZE;
