@@ -1,11 +1,12 @@
 """The Kipezen design on the GPU against the plain implementation of ``tests/plain_kipezen.py``:
 each mechanism alone (``tests/kipezen_mechanisms.py``: one-layer models whose weights and prompts
 make a wrong edge, a lost state or a left-out group show, under every cutting of the engine's step
-function), then whole models through ``bin/trace_run`` (whole prompts, the last tokens one by one over
+function), then whole models under the same cuttings (whole prompts, the last tokens one by one over
 more tokens than the windows are long, portions down to two tokens, mixed batches in a pool so small
-that pages and slots are used again), in float32 and bfloat16, the router and the experts' products
-against their equations at sizes the one-layer models do not reach, and greedy generation through
-``Engine.generate``."""
+that pages and slots are used again): float32 through ``bin/trace_run``, bfloat16 through the step
+function in this process, where the router's choices can be read and followed; the router and the
+experts' products against their equations at sizes the one-layer models do not reach; and greedy
+generation through ``Engine.generate``."""
 
 import pytest
 import torch
