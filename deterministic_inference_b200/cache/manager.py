@@ -31,7 +31,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from ..parts.spec import CompositeSpec, PagedKVSpec, StateSpec, flatten_cache_specs
+from ..parts.spec import PagedKVSpec, StateSpec, composite_cache_ids, flatten_cache_specs
 
 NULL_PAGE = 0
 
@@ -206,8 +206,8 @@ class CacheManager:
         by_key: dict[tuple, list] = {}
         specs: dict[tuple, object] = {}
         # a composite cache's members live in the groups of their own kinds, under (id, member)
-        self._composite: dict[int, int] = {cid: len(spec.members) for cid, spec in cache_specs.items()
-                                           if isinstance(spec, CompositeSpec)}
+        # (a member may be a composite itself)
+        self._composite: dict = composite_cache_ids(cache_specs)
         for cid, spec in flatten_cache_specs(cache_specs).items():
             by_key.setdefault(spec.group_key(), []).append(cid)
             specs[spec.group_key()] = spec
@@ -361,7 +361,8 @@ class CacheManager:
     def view(self, cache_id, step, writes: bool = True) -> CacheView:
         if cache_id in self._composite:
             return CacheView(writes=writes, members=[
-                self.view((cache_id, mi), step, writes) if (cache_id, mi) in self._where else None
+                self.view((cache_id, mi), step, writes)
+                if (cache_id, mi) in self._where or (cache_id, mi) in self._composite else None
                 for mi in range(self._composite[cache_id])])
         g, i = self._where[cache_id]
         if isinstance(g, PageGroup):

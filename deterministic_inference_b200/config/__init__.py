@@ -3,3 +3,4 @@ from .model_config import ConfigError, Qwen3Config, preset, preset_names
 from .gamilorn_config import GamilornConfig
 from .zatirax_config import ZatiraxConfig
 from .kipezen_config import KipezenConfig
+from .bovitar_config import BovitarConfig

@@ -11,11 +11,13 @@
 // with Dv_stored == 0 nothing is stored for values and a key's first Dv elements are its value
 // (a latent cache: one row per token serves as the key of every head and, in part, as the value).
 //
+// softcap > 0: a score s (after the scale) becomes softcap * tanh(s / softcap) before the softmax.
+//
 // Arithmetic: scores, the softmax, norms, angles and sums are float32 (expf, cosf, sinf; no fast
 // intrinsics) in the kernels of this file's first half, which take every size; the tensor-core
 // forms (masked_attention_mma.cuh) take bfloat16 sizes that are multiples of 16.  Keys are visited
 // in tiles anchored at position 0, so the order of a query's sums depends on its position alone.
-#include "source.cuh"
+#include "conv_tail.cuh"
 #include "masked_attention_mma.cuh"
 
 namespace {
@@ -98,6 +100,11 @@ attn_prepare_kernel(Source proj, long long row_width, T* __restrict__ q_out, T* 
 // of k runs per head (whole == 0, weights of D elements) or over all heads of the projection at once
 // (whole == 1, weights of Hq * D and Hkv * D elements); the rotation pairs element i with i + rot/2
 // (pairs == 0) or element 2i with 2i + 1 (pairs == 1), angle = position * freq[i].
+// cw given ([nq + nk + nv][taps] float32, the last tap the current token's): every channel of [q | k | v]
+// first passes a causal convolution over the sequence's tokens, y_t = sum_j cw[c][j] u_(t - taps + 1 + j),
+// with zeros before the sequence's start; the inputs before the step's first token come from the tail
+// of the sequence's state slot ([taps - 1][channels] float32, oldest first; slot 0 has none).  The
+// convolution's sums stay float32 into the norm.
 constexpr int ROW_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
@@ -105,20 +112,46 @@ attn_prepare_row_kernel(Source proj, long long row_width, const float* __restric
                         T* __restrict__ cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
                         int whole, float eps, const float* __restrict__ freq, int rot, int pairs,
                         const int* __restrict__ positions, const int* __restrict__ slot_mapping, int Hq, int Hkv,
-                        int D, int Dv, int page_size, long long num_pages) {
+                        int D, int Dv, int page_size, long long num_pages, const float* __restrict__ cw, int taps,
+                        const float* state, long long slot_stride, long long tail_at,
+                        const int* __restrict__ token_seq, const int* __restrict__ cu_q_lens,
+                        const int* __restrict__ state_slots) {
   extern __shared__ float smem[];      // the row's [q | k | v] (nq + nk + nv floats), then a factor per q and k head
   __shared__ float scratch[32];
-  pdl_prologue(proj.p);
+  pdl_prologue(proj.p, state);
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = Hq * D, nk = Hkv * D, nv = Hkv * Dv;
   float* x = smem;
   float* factor = smem + nq + nk + nv;
   const long long row = (long long)t * row_width;
-  for (int i = threadIdx.x; i < nq + nk + nv; i += ROW_THREADS) {
-    float v = source_load(proj, row + i);
-    if (bias != nullptr) v = __fadd_rn(v, bias[i]);
-    x[i] = round_to<T>(v);
+  if (cw != nullptr) {
+    const int CH = nq + nk + nv;
+    const int b = token_seq[t];
+    const int local = t - cu_q_lens[b];
+    const long long slot = state_slots[b];
+    const float* tail = slot != 0 ? state + slot * slot_stride + tail_at : nullptr;
+    for (int i = threadIdx.x; i < CH; i += ROW_THREADS) {
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {          // tap j reads the input taps - 1 - j tokens back
+        const int back = taps - 1 - j;
+        float u;
+        if (back <= local) {
+          u = source_load(proj, (long long)(t - back) * row_width + i);
+          if (bias != nullptr) u = __fadd_rn(u, bias[i]);
+        } else {
+          u = tail != nullptr ? tail[(long long)(taps - 1 - (back - local)) * CH + i] : 0.f;
+        }
+        acc = __fmaf_rn(cw[(long long)i * taps + j], u, acc);
+      }
+      x[i] = acc;
+    }
+  } else {
+    for (int i = threadIdx.x; i < nq + nk + nv; i += ROW_THREADS) {
+      float v = source_load(proj, row + i);
+      if (bias != nullptr) v = __fadd_rn(v, bias[i]);
+      x[i] = round_to<T>(v);
+    }
   }
   __syncthreads();
   if (q_w != nullptr) {
@@ -290,7 +323,7 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
                         const int* __restrict__ token_seq, const int* __restrict__ positions,
                         int T_tokens, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
                         float scale, int mask_kind, int mask_size, int keep, const float* __restrict__ sink,
-                        Source gate, long long gate_row, long long gate_col) {
+                        Source gate, long long gate_row, long long gate_col, float softcap) {
   extern __shared__ float smem[];
   pdl_prologue(q, cache, block_table, token_seq, positions, gate.p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -331,6 +364,7 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
       float dot = 0.f;
       for (int d = 0; d < Dk; ++d) dot = __fmaf_rn(sq[d], Elem<T>::load(krow + d), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = visible ? expf(s - m_new) : 0.f;
@@ -385,13 +419,13 @@ int launch_masked_attention(const void* q, void* out, const void* cache, const i
                             int max_blocks, const int* token_seq, const int* positions, int T_tokens, int Hq,
                             int Hkv, int Dk, int Dv, int Dv_stored, int page_size, float scale, int mask_kind,
                             int mask_size, int keep, const float* sink, Source gate, long long gate_row,
-                            long long gate_col, cudaStream_t st) {
+                            long long gate_col, float softcap, cudaStream_t st) {
   const int blocks = ceil_div_host((long long)T_tokens * Hq, WARPS);
   const size_t smem = (size_t)WARPS * Dk * sizeof(float);
 #define DIB_MA(NV)                                                                                       \
   dib_launch(masked_attention_kernel<T, NV>, dim3(blocks), dim3(WARPS * 32), smem, st, (const T*)q, (T*)out, \
              (const T*)cache, block_table, max_blocks, token_seq, positions, T_tokens, Hq, Hkv, Dk, Dv,   \
-             Dv_stored, page_size, scale, mask_kind, mask_size, keep, sink, gate, gate_row, gate_col)
+             Dv_stored, page_size, scale, mask_kind, mask_size, keep, sink, gate, gate_row, gate_col, softcap)
   if (Dv <= 64) DIB_MA(2);
   else if (Dv <= 128) DIB_MA(4);
   else if (Dv <= 256) DIB_MA(8);
@@ -436,9 +470,14 @@ int dib_attn_prepare_row(const void* proj, int kind, int splits, long long strid
                          const float* bias, void* q_out, void* cache, const float* q_w, const float* k_w, int whole,
                          float eps, const float* freq, int rot, int pairs, const int* positions,
                          const int* slot_mapping, int T, int Hq, int Hkv, int D, int Dv, int page_size,
-                         long long num_pages, int dtype, cudaStream_t st) {
+                         long long num_pages, int dtype, const float* cw, int taps, float* state,
+                         long long slot_stride, long long tail_at, const int* token_seq, const int* cu_q_lens,
+                         const int* state_slots, int B, cudaStream_t st) {
   if (T == 0) return DIB_OK;
   if (D < 1 || Dv < 1 || Hq < 1 || Hkv < 1 || rot < 0 || rot > D || rot % 2 || page_size < 1) return DIB_BAD_SIZE;
+  if (cw != nullptr && (taps < 1 || taps > 64 || token_seq == nullptr || cu_q_lens == nullptr ||
+                        state_slots == nullptr || (taps > 1 && state == nullptr)))
+    return DIB_BAD_SIZE;
   if (freq == nullptr) rot = 0;
   const size_t smem = sizeof(float) * ((size_t)Hq * D + (size_t)Hkv * (D + Dv) + Hq + Hkv);
   if (smem > 200 * 1024) return DIB_BAD_SIZE;
@@ -452,7 +491,8 @@ int dib_attn_prepare_row(const void* proj, int kind, int splits, long long strid
     }
     dib_launch(attn_prepare_row_kernel<float>, dim3(T), dim3(ROW_THREADS), smem, st, src, row_width, bias,
                (float*)q_out, (float*)cache, q_w, k_w, whole, eps, freq, rot, pairs, positions, slot_mapping, Hq, Hkv,
-               D, Dv, page_size, num_pages);
+               D, Dv, page_size, num_pages, cw, taps, (const float*)state, slot_stride, tail_at, token_seq, cu_q_lens,
+               state_slots);
   } else if (dtype == 1) {
     if (smem > 48 * 1024 && !once16.done()) {
       if (cudaFuncSetAttribute(attn_prepare_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -461,9 +501,16 @@ int dib_attn_prepare_row(const void* proj, int kind, int splits, long long strid
     }
     dib_launch(attn_prepare_row_kernel<__nv_bfloat16>, dim3(T), dim3(ROW_THREADS), smem, st, src, row_width, bias,
                (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, q_w, k_w, whole, eps, freq, rot, pairs, positions,
-               slot_mapping, Hq, Hkv, D, Dv, page_size, num_pages);
+               slot_mapping, Hq, Hkv, D, Dv, page_size, num_pages, cw, taps, (const float*)state, slot_stride, tail_at,
+               token_seq, cu_q_lens, state_slots);
   } else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
+  if (cw != nullptr && taps > 1 && B > 0) {
+    // the convolutions' tails move on by the step's tokens, once every row has read them
+    dib_launch(conv_tail_update_kernel, dim3(B), dim3(256), 0, st, src, row_width, 0ll, bias, state, slot_stride,
+               tail_at, cu_q_lens, state_slots, Hq * D + Hkv * (D + Dv), taps);
+    DIB_CHECK_LAUNCH();
+  }
   return DIB_OK;
 }
 
@@ -538,7 +585,7 @@ int dib_masked_attention_mma(const void* q, void* out, const void* cache, const 
                              float scale, int mask_kind, int mask_size, int keep, const void* gate, int gate_kind,
                              int gate_splits, long long gate_stride, long long gate_row, long long gate_col,
                              int rows, float* partial_o, float* partial_ml, int chunk_tiles, int max_chunks,
-                             int num_tokens, cudaStream_t st) {
+                             int num_tokens, float softcap, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (Dk < 16 || Dk % 16 || Dv < 16 || Dv % 16 || Dv > 256 || Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > rows ||
       (rows != 64 && rows != 128) || page_size < 1 || mask_kind < 0 || mask_kind > 2 ||
@@ -550,7 +597,7 @@ int dib_masked_attention_mma(const void* q, void* out, const void* cache, const 
 #define DIB_MAM(NV, ROWS)                                                                                    \
   return ma_mma::launch<NV, ROWS>(q, out, cache, block_table, max_blocks, positions, seq_lens, cu_q_lens, tiles, num_tiles, \
                                   sink, Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, keep, g, \
-                                  gate_row, gate_col, partial_o, partial_ml, chunk_tiles, max_chunks, num_tokens, st)
+                                  gate_row, gate_col, partial_o, partial_ml, chunk_tiles, max_chunks, num_tokens, softcap, st)
   const int nv = (Dv + 63) / 64;
   if (rows == 64) {
     if (nv == 1) DIB_MAM(4, 64);
@@ -571,7 +618,7 @@ int dib_masked_attention(const void* q, void* out, const void* cache, const int*
                          const int* token_seq, const int* positions, int T, int Hq, int Hkv, int Dk, int Dv,
                          int Dv_stored, int page_size, float scale, int mask_kind, int mask_size, int keep,
                          const float* sink, const void* gate, int gate_kind, int gate_splits,
-                         long long gate_stride, long long gate_row, long long gate_col, int dtype,
+                         long long gate_stride, long long gate_row, long long gate_col, int dtype, float softcap,
                          cudaStream_t st) {
   if (T == 0) return DIB_OK;
   if (Dk < 1 || Dk > 2048 || Dv < 1 || Dv > 1024 || Hkv < 1 || Hq % Hkv != 0 || page_size < 1 ||
@@ -582,11 +629,11 @@ int dib_masked_attention(const void* q, void* out, const void* cache, const int*
   if (dtype == 0)
     return launch_masked_attention<float>(q, out, cache, block_table, max_blocks, token_seq, positions, T, Hq,
                                           Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, keep, sink, g,
-                                          gate_row, gate_col, st);
+                                          gate_row, gate_col, softcap, st);
   if (dtype == 1)
     return launch_masked_attention<__nv_bfloat16>(q, out, cache, block_table, max_blocks, token_seq, positions, T,
                                                   Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind,
-                                                  mask_size, keep, sink, g, gate_row, gate_col, st);
+                                                  mask_size, keep, sink, g, gate_row, gate_col, softcap, st);
   return DIB_BAD_DTYPE;
 }
 

@@ -63,7 +63,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
                             int VD, int VD_stored,
                             int page_size, float scale, int mask_kind, int mask_size, int keep, Source gate,
                             long long gate_row, long long gate_col, float* partial_o, float* partial_ml,
-                            int chunk_tiles, int max_chunks) {
+                            int chunk_tiles, int max_chunks, float softcap) {
   extern __shared__ __align__(16) unsigned char mam_smem[];
   const int R = Hq / Hkv;
   const bool in_keys = VD_stored == 0;
@@ -206,7 +206,9 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
           const int h = e >> 1;
           const int j = k0 + n * 8 + tig * 2 + (e & 1);
           const bool sees = j <= row_pos[h] && (j >= row_lo[h] || j < keep);
-          s[n][e] = sees ? s[n][e] * scale_log2 : MA_NEG_BIG;
+          // (softcap > 0: the scaled score passes softcap * tanh(. / softcap), float32, before the softmax)
+          const float sc = softcap > 0.f ? softcap * tanhf(s[n][e] * scale / softcap) * MA_LOG2E : s[n][e] * scale_log2;
+          s[n][e] = sees ? sc : MA_NEG_BIG;
           mx[h] = fmaxf(mx[h], s[n][e]);
         }
       float alpha[2], ref[2];
@@ -358,7 +360,7 @@ static int launch(const void* q, void* out, const void* cache, const int* block_
                   const int* positions, const int* seq_lens, const int* cu_q_lens, const int* tiles, int num_tiles,
                   const float* sink, int Hq, int Hkv, int D, int VD, int VD_stored, int page_size, float scale, int mask_kind,
                   int mask_size, int keep, Source gate, long long gate_row, long long gate_col, float* partial_o,
-                  float* partial_ml, int chunk_tiles, int max_chunks, int num_tokens, cudaStream_t st) {
+                  float* partial_ml, int chunk_tiles, int max_chunks, int num_tokens, float softcap, cudaStream_t st) {
   const size_t smem = smem_bytes(D, VD, VD_stored, ROWS);
   if (smem > MAX_DYNAMIC_SMEM) return DIB_BAD_SIZE;
   const bool chunked = partial_o != nullptr && max_chunks > 1;
@@ -373,7 +375,7 @@ static int launch(const void* q, void* out, const void* cache, const int* block_
              smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table,
              bt_width, positions, seq_lens, cu_q_lens, tiles, sink, Hq, Hkv, D, VD, VD_stored, page_size, scale, mask_kind,
              mask_size, keep, gate, gate_row, gate_col, chunked ? partial_o : (float*)nullptr,
-             chunked ? partial_ml : (float*)nullptr, chunk_tiles, max_chunks);
+             chunked ? partial_ml : (float*)nullptr, chunk_tiles, max_chunks, softcap);
   DIB_CHECK_LAUNCH();
   if (chunked) {
     dib_launch(masked_attention_merge_kernel, dim3(num_tokens, Hq), dim3(VD >= 128 ? 128 : 64), 0, st,

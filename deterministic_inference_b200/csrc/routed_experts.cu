@@ -1,16 +1,17 @@
 // A feed-forward of routed experts: the router's choice, the sort of (token, expert) pairs into
 // tiles of one expert each, the two grouped products, and the weighted sum.
 //
-//   route:    s = sigmoid(z); choice = s + correction; experts in equal groups of neighbours, a
-//             group's score the sum of its two largest choice scores, the best `group_keep` groups
-//             stay; of their experts the `top` largest choice scores win (ties: the lower index);
-//             weight_j = s_j / (sum of the chosen s + eps) * scale.  One warp per token, float32.
+//   route:    s = sigmoid(z), or softmax(z) over all experts (score_kind 1); choice = s + correction;
+//             experts in equal groups of neighbours, a group's score the sum of its `group_top` (1 or
+//             2) largest choice scores, the best `group_keep` groups stay; of their experts the `top`
+//             largest choice scores win (ties: the lower index); weight_j = s_j / (sum of the chosen
+//             s + eps) * scale, or s_j * scale (normalize 0).  One warp per token, float32.
 //   sort:     pairs p = t * top + j are placed, by expert, into tiles of `tile` rows; an expert's
 //             rows are filled up to whole tiles (row -> pair or -1; tile -> expert or -1).
 //   gate/up:  hidden[row] = silu(x[token] Wg_e^T) * (x[token] Wu_e^T), rounded once to x's type.
 //   down:     per_pair[pair] = hidden[row] Wd_e^T, float32.
 //   combine:  out[t] = sum_j weight[t, j] per_pair[t * top + j] (in the order of j)
-//                      + sigmoid(logits[t, col]) * shared[t].
+//                      + sigmoid(logits[t, col]) * shared[t] (col < 0: + shared[t]).
 //
 // A row's sums never depend on the other rows of its tile, on the tile's size or on where the row
 // sits in it: bfloat16 products run on the tensor cores (mma.sync m16n8k16, float32 accumulators,
@@ -38,7 +39,8 @@ __device__ __forceinline__ void warp_arg_best(float& v, int& i) {
 constexpr int ROUTE_WARPS = 4;
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(Source logits, long long row_width, const float* __restrict__ correction, int* __restrict__ ids,
-                 float* __restrict__ weights, int T, int E, int top, int groups, int keep, float scale, float eps) {
+                 float* __restrict__ weights, int T, int E, int top, int groups, int keep, float scale, float eps,
+                 int score_kind, int group_top, int normalize) {
   extern __shared__ float smem[];            // per warp: s [E], choice [E], group score [groups]
   pdl_prologue(logits.p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,10 +50,33 @@ moe_route_kernel(Source logits, long long row_width, const float* __restrict__ c
   float* choice = s + E;
   float* gscore = choice + E;
   const int per = E / groups;
-  for (int e = lane; e < E; e += 32) {
-    const float v = sigmoid_f32(source_load(logits, (long long)t * row_width + e));
-    s[e] = v;
-    choice[e] = __fadd_rn(v, correction[e]);
+  if (score_kind == 1) {
+    // softmax over all experts: the largest logit, then the sum of the exponentials in a fixed order
+    float mx = NEG_INF;
+    for (int e = lane; e < E; e += 32) {
+      const float z = source_load(logits, (long long)t * row_width + e);
+      s[e] = z;
+      mx = fmaxf(mx, z);
+    }
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(s[e] - mx);
+      s[e] = v;
+      den = __fadd_rn(den, v);
+    }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) {
+      const float v = s[e] / den;
+      s[e] = v;
+      choice[e] = __fadd_rn(v, correction[e]);
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float v = sigmoid_f32(source_load(logits, (long long)t * row_width + e));
+      s[e] = v;
+      choice[e] = __fadd_rn(v, correction[e]);
+    }
   }
   __syncwarp();
   if (groups > 1) {
@@ -62,7 +87,7 @@ moe_route_kernel(Source logits, long long row_width, const float* __restrict__ c
         if (c > a) { b = a; a = c; }
         else if (c > b) b = c;
       }
-      gscore[g] = per > 1 ? __fadd_rn(a, b) : a;
+      gscore[g] = (per > 1 && group_top > 1) ? __fadd_rn(a, b) : a;
     }
     __syncwarp();
     // the best `keep` groups, one after the other; a kept group's score is replaced by +infinity
@@ -101,7 +126,7 @@ moe_route_kernel(Source logits, long long row_width, const float* __restrict__ c
   }
   if (lane < top) {
     ids[(long long)t * top + lane] = mine_id;
-    weights[(long long)t * top + lane] = mine / __fadd_rn(sum, eps) * scale;
+    weights[(long long)t * top + lane] = normalize ? mine / __fadd_rn(sum, eps) * scale : __fmul_rn(mine, scale);
   }
 }
 
@@ -336,6 +361,7 @@ moe_product_kernel(const T* __restrict__ a_rows, const int* __restrict__ order, 
 }
 
 // out[t, c] = sum_j weights[t, j] * per_pair[t * top + j, c], j ascending, + sigmoid(gate[t]) * shared[t, c]
+// (gate_col < 0: the shared expert has no gate and is added as it is)
 __global__ void moe_combine_kernel(const float* __restrict__ per_pair, const float* __restrict__ weights, Source shared,
                                    Source logits, long long logit_row, int gate_col, float* __restrict__ out, int T,
                                    int top, int W) {
@@ -346,7 +372,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ per_pair, const flo
     float v = 0.f;
     for (int j = 0; j < top; ++j) v = __fmaf_rn(weights[t * top + j], per_pair[(t * top + j) * W + c], v);
     if (shared.p != nullptr)
-      v = __fmaf_rn(sigmoid_f32(source_load(logits, t * logit_row + gate_col)), source_load(shared, i), v);
+      v = gate_col < 0 ? __fadd_rn(v, source_load(shared, i))
+                       : __fmaf_rn(sigmoid_f32(source_load(logits, t * logit_row + gate_col)), source_load(shared, i), v);
     out[i] = v;
   }
 }
@@ -452,15 +479,15 @@ int dib_moe_scatter_rows(const float* y_sorted, const int* order, long long rows
 
 int dib_moe_route(const void* logits, int kind, int splits, long long stride, long long row_width,
                   const float* correction, int* ids, float* weights, int T, int E, int top, int groups, int keep,
-                  float scale, float eps, cudaStream_t st) {
+                  float scale, float eps, int score_kind, int group_top, int normalize, cudaStream_t st) {
   if (T == 0) return DIB_OK;
   if (E < 1 || E > 1024 || top < 1 || top > 32 || groups < 1 || E % groups || keep < 1 || keep > groups ||
-      top > keep * (E / groups))
+      top > keep * (E / groups) || score_kind < 0 || score_kind > 1 || group_top < 1 || group_top > 2)
     return DIB_BAD_SIZE;
   const size_t smem = sizeof(float) * ROUTE_WARPS * (2 * (size_t)E + groups);
   dib_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, st,
              make_source(logits, kind, splits, stride), row_width, correction, ids, weights, T, E, top, groups, keep,
-             scale, eps);
+             scale, eps, score_kind, group_top, normalize);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

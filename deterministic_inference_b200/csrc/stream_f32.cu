@@ -155,6 +155,54 @@ __global__ void stream_norm_kernel(float* residual, Source x0, float a0, Source 
     store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
 }
 
+// One block per row, every term normed before it joins the stream:
+// residual[row] += a0 * x0[row] / sqrt(mean(x0[row]^2) + e0) * w0 (+ a1 * x1[row] / sqrt(mean(x1[row]^2) + e1) * w1),
+// the terms' sum taken first and then added, nothing rounded below float32; then, when out is given,
+// out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps) * w.  A term without a weight (w0 null)
+// joins as a0 * x0.  The block's width depends on W alone.
+__global__ void stream_norm_normed_terms_kernel(float* residual, int terms, Source x0, float a0, const float* w0,
+                                                float e0, Source x1, float a1, const float* w1, float e1,
+                                                const float* w, void* out, int out_dtype, int W, float eps) {
+  __shared__ float scratch[32];
+  pdl_prologue(x0.p, x1.p);
+  const long long base = (long long)blockIdx.x * W;
+  float r0 = 1.f, r1 = 1.f;
+  if (w0 != nullptr) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float v = source_load(x0, base + c);
+      s = __fmaf_rn(v, v, s);
+    }
+    r0 = 1.0f / sqrtf(block_sum(s, scratch) / (float)W + e0);
+  }
+  if (terms >= 2 && w1 != nullptr) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float v = source_load(x1, base + c);
+      s = __fmaf_rn(v, v, s);
+    }
+    r1 = 1.0f / sqrtf(block_sum(s, scratch) / (float)W + e1);
+  }
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = source_load(x0, base + c);
+    if (w0 != nullptr) v = v * r0 * w0[c];
+    float sum = __fmul_rn(a0, v);
+    if (terms >= 2) {
+      float u = source_load(x1, base + c);
+      if (w1 != nullptr) u = u * r1 * w1[c];
+      sum = __fmaf_rn(a1, u, sum);
+    }
+    const float r = __fadd_rn(residual[base + c], sum);
+    residual[base + c] = r;
+    ss = __fmaf_rn(r, r, ss);
+  }
+  if (out == nullptr) return;
+  const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
+}
+
 // out = a0 * x0 (+ a1 * x1), float32
 __global__ void weighted_sum_kernel(Source x0, float a0, Source x1, float a1, int terms, float* out,
                                     long long n) {
@@ -185,6 +233,14 @@ __global__ void softcap_kernel(float* x, float cap, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
     x[i] = cap * tanhf(x[i] / cap);
+}
+
+// x = x * a, in place
+__global__ void scale_kernel(float* x, float a, long long n) {
+  pdl_prologue();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    x[i] = __fmul_rn(x[i], a);
 }
 
 static inline int flat_grid(long long n, int block) {
@@ -266,6 +322,23 @@ int dib_stream_norm(float* residual, int terms, const void* x0, int kind0, int s
   return DIB_OK;
 }
 
+// Terms that are normed on their way into the stream (w0 / w1 null: that term joins as it is).
+// out null: the stream is updated and nothing is normed.
+int dib_stream_norm_normed_terms(float* residual, int terms, const void* x0, int kind0, int splits0, long long stride0,
+                                 float a0, const float* w0, float e0, const void* x1, int kind1, int splits1,
+                                 long long stride1, float a1, const float* w1, float e1, const float* w, void* out,
+                                 int out_dtype, int rows, int W, float eps, cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (W < 1 || terms < 1 || terms > 2) return DIB_BAD_SIZE;
+  if (out != nullptr && (w == nullptr || (out_dtype != 0 && out_dtype != 1))) return DIB_BAD_DTYPE;
+  const Source s0 = make_source(x0, kind0, splits0, stride0), s1 = make_source(x1, kind1, splits1, stride1);
+  const dim3 grid(rows), block(W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
+  dib_launch(stream_norm_normed_terms_kernel, grid, block, 0, st, residual, terms, s0, a0, w0, e0, s1, a1, w1, e1, w,
+             out, out_dtype, W, eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
 int dib_weighted_sum(int terms, const void* x0, int kind0, int splits0, long long stride0, float a0,
                      const void* x1, int kind1, int splits1, long long stride1, float a1, float* out,
                      long long n, cudaStream_t st) {
@@ -284,6 +357,13 @@ int dib_xielu(const void* z, int kind, int splits, long long stride, float ap, f
   if (out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
   dib_launch(xielu_kernel, dim3(flat_grid(n, 256)), dim3(256), 0, st, make_source(z, kind, splits, stride), ap,
              an, out, out_dtype, n);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_scale(float* x, float a, long long n, cudaStream_t st) {
+  if (n == 0) return DIB_OK;
+  dib_launch(scale_kernel, dim3(flat_grid(n, 256)), dim3(256), 0, st, x, a, n);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

@@ -45,6 +45,7 @@ SOURCES = {
     "masked_attention": "masked_attention.cu",
     "linear_recurrence": "linear_recurrence.cu",
     "routed_experts": "routed_experts.cu",
+    "state_space": "state_space.cu",
 }
 HEADERS = ("common.cuh", "attention_merge.cuh")
 # further headers a library includes
@@ -55,7 +56,8 @@ EXTRA_HEADERS = {
     "stream_f32": ("source.cuh",),
     "sigmoid_attention": ("source.cuh", "sigmoid_attention_mma.cuh"),
     "delta_rule": ("source.cuh", "conv_tail.cuh"),
-    "masked_attention": ("source.cuh", "masked_attention_mma.cuh", "sigmoid_attention_mma.cuh"),
+    "masked_attention": ("source.cuh", "masked_attention_mma.cuh", "sigmoid_attention_mma.cuh", "conv_tail.cuh"),
+    "state_space": ("source.cuh", "conv_tail.cuh"),
     "linear_recurrence": ("source.cuh", "conv_tail.cuh"),
     "routed_experts": ("source.cuh",),
 }

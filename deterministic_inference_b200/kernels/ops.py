@@ -260,7 +260,8 @@ class SplitAttention:
 
 class WeightedSum:
     """sum_i scale_i * term_i that is not computed yet: the outputs of mixers that run side
-    by side, each a tensor or a ``SplitSum``.  The norm of a float32 residual stream adds
+    by side, each a tensor, a ``SplitSum`` or a ``NormedTerm`` (an output that is RMS-normed
+    with a weight of its own before it is scaled).  The norm of a float32 residual stream adds
     the terms to the stream in their order while it loads them; ``tensor()`` gives the sum
     as a float32 tensor."""
 
@@ -278,8 +279,16 @@ class WeightedSum:
     def device(self):
         return self.terms[0][1].device
 
+    @property
+    def normed(self) -> bool:
+        return any(isinstance(x, NormedTerm) for _, x in self.terms)
+
     def tensor(self) -> torch.Tensor:
         rows, width = self.shape
+        if self.normed:
+            out = torch.zeros(rows, width, dtype=torch.float32, device=self.device)
+            _stream_add_normed_terms(out, self.terms, None, 0.0, None)
+            return out
         out = torch.empty(rows, width, dtype=torch.float32, device=self.device)
         st = _lib("stream_f32").dib_weighted_sum(c_int(len(self.terms)), *_terms_args(self.terms, 2),
                                                  _ptr(out), c_longlong(rows * width), _stream())
@@ -336,6 +345,31 @@ def _terms_args(terms: list, n: int) -> list:
         else:
             out += [c_void_p(0), c_int(0), c_int(1), c_longlong(0), c_float(0.0)]
     return out
+
+
+def _stream_add_normed_terms(stream: torch.Tensor, terms: list, weight, eps: float, out) -> None:
+    """stream += sum_i a_i * n_i in place (float32), n_i a ``NormedTerm`` (x / rms(x) * its weight) or a
+    plain term; with ``out`` also out = RMSNorm(stream) * weight."""
+    rows, w = stream.shape
+    args = []
+    for i in range(2):
+        if i < len(terms):
+            a, x = terms[i]
+            if tuple(x.shape) != (rows, w):
+                raise KernelError(f"a term of shape {tuple(x.shape)} for a stream {(rows, w)}")
+            if isinstance(x, NormedTerm):
+                _need(x.weight, "term.weight", torch.float32, 1)
+                if x.weight.shape[0] != w:
+                    raise KernelError(f"a normed term's weight has {x.weight.shape[0]} elements, rows have {w}")
+                args += [*_source_args(x.x), c_float(a), _ptr(x.weight), c_float(x.eps)]
+            else:
+                args += [*_source_args(x), c_float(a), c_void_p(0), c_float(0.0)]
+        else:
+            args += [c_void_p(0), c_int(0), c_int(1), c_longlong(0), c_float(0.0), c_void_p(0), c_float(0.0)]
+    st = _lib("stream_f32").dib_stream_norm_normed_terms(
+        _ptr(stream), c_int(len(terms)), *args, _ptr(weight), _ptr(out),
+        c_int(_DT[out.dtype] if out is not None else 0), c_int(rows), c_int(w), c_float(eps), _stream())
+    _check(st, "stream_rms_norm(normed terms)", f"row width {w}")
 
 
 def as_tensor(x):
@@ -594,6 +628,8 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """out[r] = x[index[r]]; index int32."""
     if isinstance(x, NormedTerm):          # a norm works row by row: gather first
         return NormedTerm(gather_rows(x.x, index), x.weight, x.eps)
+    if isinstance(x, WeightedSum) and x.normed:
+        return WeightedSum([(a, gather_rows(term, index)) for a, term in x.terms])
     x = as_tensor(x)
     _need(x, "x", None, 2)
     _need(index, "index", torch.int32, 1)
@@ -771,6 +807,10 @@ def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_
         out = torch.empty(rows, w, dtype=out_dtype, device=stream.device)
         stream_add_(stream, add, norm_weight=weight, norm_eps=eps, out=out)
         return out
+    if isinstance(add, WeightedSum) and add.normed:
+        out = torch.empty(rows, w, dtype=out_dtype, device=stream.device)
+        _stream_add_normed_terms(stream, add.terms, weight, eps, out)
+        return out
     terms = []
     if add is not None:
         terms = add.terms if isinstance(add, WeightedSum) else [(1.0, add)]
@@ -859,6 +899,14 @@ def xielu(z, alpha_p: float, alpha_n: float, out_dtype) -> torch.Tensor:
                                       c_int(_DT[out_dtype]), c_longlong(rows * w), _stream())
     _check(st, "xielu")
     return out
+
+
+def scale_(x: torch.Tensor, a: float) -> torch.Tensor:
+    """x *= a in place (float32)."""
+    _need(x, "x", torch.float32)
+    st = _lib("stream_f32").dib_scale(_ptr(x), c_float(a), c_longlong(x.numel()), _stream())
+    _check(st, "scale_")
+    return x
 
 
 def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
@@ -1118,6 +1166,63 @@ def gated_delta_rule(proj, conv_weight: torch.Tensor, a_log: torch.Tensor, dt_bi
     return out
 
 
+# ---------------------------------------------------------------- state-space recurrence, a scalar decay per head
+
+def state_space(proj, conv_weight: torch.Tensor, conv_bias, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                d_skip: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor, step, num_heads: int,
+                head_dim: int, state_dim: int, groups: int, norm_groups: int, taps: int, norm_eps: float,
+                out_dtype) -> torch.Tensor:
+    """A state-space recurrence with a scalar decay per head over every sequence's tokens of the step:
+    [T, H * P] in ``out_dtype``.  ``proj`` rows are [z: H P | x: H P | B: G N | C: G N | dt: H | padding].
+    x, B and C together pass a causal convolution per channel (``conv_weight`` float32 [H P + 2 G N, taps],
+    the last tap the current token's; the inputs before the step's first token come from the state's tail),
+    ``conv_bias`` and silu; dt = softplus(dt + dt_bias); per head h (B and C of group h // (H / G)) with S
+    [N, P] from zero: S <- exp(-exp(a_log[h]) dt) S + dt B x^T, y = S^T C + d_skip[h] x.  Then y * silu(z),
+    RMS-normed in ``norm_groups`` equal parts (``norm_eps``), times ``norm_weight`` [H P].  ``state`` float32
+    [slots, H N P + (taps - 1) channels]: the heads' states, then the convolution's last taps - 1 inputs
+    (rows ``step.state_slots``)."""
+    t, width = proj.shape
+    h, p, n, g = num_heads, head_dim, state_dim, groups
+    inner, chan = h * p, h * p + 2 * g * n
+    if width < inner + chan + h:
+        raise KernelError(f"state_space: projection rows of {width}, expected at least {inner + chan + h}")
+    _need(conv_weight, "conv_weight", torch.float32, 2)
+    for name, v, size in (("a_log", a_log, h), ("dt_bias", dt_bias, h), ("d_skip", d_skip, h),
+                          ("norm_weight", norm_weight, inner)):
+        _need(v, name, torch.float32, 1)
+        if v.shape[0] != size:
+            raise KernelError(f"state_space: {name} has {v.shape[0]} elements, expected {size}")
+    if conv_bias is not None:
+        _need(conv_bias, "conv_bias", torch.float32, 1)
+    _need(state, "state", torch.float32, 2)
+    if tuple(conv_weight.shape) != (chan, taps) or (conv_bias is not None and conv_bias.shape[0] != chan) \
+            or state.shape[1] != h * n * p + (taps - 1) * chan or h % g or inner % norm_groups:
+        raise KernelError("state_space: a weight or the state does not fit the head counts and sizes")
+    lib = _lib("state_space")
+    src = _source_args(proj)
+    dev = state.device
+    slot_stride, tail_at = state.shape[1], h * n * p
+    xbc = torch.empty(t, chan, dtype=torch.float32, device=dev)
+    dtv = torch.empty(t, h, 2, dtype=torch.float32, device=dev)
+    st = lib.dib_ssm_prepare(*src, c_longlong(width), _ptr(conv_weight), _ptr(conv_bias), _ptr(a_log), _ptr(dt_bias),
+                             _ptr(state), c_longlong(slot_stride), c_longlong(tail_at), _ptr(step.token_seq),
+                             _ptr(step.cu_q_lens), _ptr(step.state_slots), _ptr(xbc), _ptr(dtv), c_int(t), c_int(h),
+                             c_int(g), c_int(n), c_int(p), c_int(taps), _stream())
+    _check(st, "state_space(prepare)", f"{h} heads of {p} in {g} groups, state {n}, {taps} taps")
+    y = torch.empty(t, inner, dtype=torch.float32, device=dev)
+    st = lib.dib_ssm_recurrence(_ptr(xbc), _ptr(dtv), _ptr(d_skip), _ptr(state), c_longlong(slot_stride), _ptr(y),
+                                _ptr(step.cu_q_lens), _ptr(step.state_slots), c_int(step.num_seqs), c_int(h),
+                                c_int(g), c_int(n), c_int(p), _stream())
+    _check(st, "state_space(recurrence)", f"state {n} (at most 256)")
+    out = torch.empty(t, inner, dtype=out_dtype, device=dev)
+    st = lib.dib_ssm_output(_ptr(y), *src, c_longlong(width), _ptr(norm_weight), _ptr(out), c_int(_DT[out_dtype]),
+                            _ptr(state), c_longlong(slot_stride), c_longlong(tail_at), _ptr(step.cu_q_lens),
+                            _ptr(step.state_slots), c_int(t), c_int(step.num_seqs), c_int(h), c_int(g), c_int(n),
+                            c_int(p), c_int(norm_groups), c_int(taps), c_float(norm_eps), _stream())
+    _check(st, "state_space(output)", kernels=2 if taps > 1 else 1)
+    return out
+
+
 # ---------------------------------------------------------------- gated linear recurrent unit
 
 def gated_linear_recurrence(proj, bias: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor,
@@ -1178,16 +1283,23 @@ EXPERT_TILE_ROWS_TC = 128
 EXPERTS_TC = __import__("os").environ.get("DIB200_EXPERTS_TC", "1") != "0"
 
 
+ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
 def route_experts(logits, correction: torch.Tensor, num_experts: int, top: int, group_count: int,
-                  group_keep: int, scale: float, eps: float):
+                  group_keep: int, scale: float, eps: float, score: str = "sigmoid", group_top: int = 2,
+                  normalize: bool = True):
     """(int32 [T, top] chosen experts, float32 [T, top] their weights).  ``logits`` [T, >= E] (a float32
-    tensor or split sums; columns from E on are not the router's): s = sigmoid(logits); the choice is
-    made on s + correction: the experts form ``group_count`` groups of neighbours, a group's score is
-    the sum of its two largest choice scores, the ``group_keep`` best groups stay, and of their experts
-    the ``top`` largest choice scores win (ties: the lower index).  Weights: s of the chosen over
-    their sum (+ eps), times ``scale``."""
+    tensor or split sums; columns from E on are not the router's): s = sigmoid(logits), or (``score``
+    "softmax") the softmax of the row's E logits; the choice is made on s + correction: the experts form
+    ``group_count`` groups of neighbours, a group's score is the sum of its ``group_top`` (1 or 2)
+    largest choice scores, the ``group_keep`` best groups stay, and of their experts the ``top`` largest
+    choice scores win (ties: the lower index).  Weights: s of the chosen over their sum (+ eps), times
+    ``scale``; with ``normalize`` off s times ``scale``."""
     t, row = logits.shape
     _need(correction, "correction", torch.float32, 1)
+    if score not in ROUTER_SCORES or group_top not in (1, 2):
+        raise KernelError(f"route_experts: score {score!r} ({sorted(ROUTER_SCORES)}) or group_top {group_top} (1, 2)")
     if correction.shape[0] != num_experts or row < num_experts or num_experts % group_count \
             or not 1 <= group_keep <= group_count or not 1 <= top <= group_keep * (num_experts // group_count):
         raise KernelError(f"route_experts: {num_experts} experts, rows of {row}, {group_count} groups, "
@@ -1197,7 +1309,8 @@ def route_experts(logits, correction: torch.Tensor, num_experts: int, top: int, 
     st = _lib("routed_experts").dib_moe_route(*_source_args(logits), c_longlong(row), _ptr(correction), _ptr(ids),
                                               _ptr(weights), c_int(t), c_int(num_experts), c_int(top),
                                               c_int(group_count), c_int(group_keep), c_float(scale), c_float(eps),
-                                              _stream())
+                                              c_int(ROUTER_SCORES[score]), c_int(group_top),
+                                              c_int(1 if normalize else 0), _stream())
     _check(st, "route_experts", f"{num_experts} experts (at most 1024), {top} chosen (at most 32)")
     return ids, weights
 
@@ -1206,7 +1319,7 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
                    w_down: torch.Tensor, shared, logits, shared_gate_col: int, out_dtype) -> torch.Tensor:
     """float32 [T, W]: sum_j weights[t, j] * down_e(silu(gate_e x_t) * up_e x_t) over the chosen experts
     e = ids[t, j], in the order of j, plus (``shared`` [T, W], a tensor or split sums, given)
-    sigmoid(logits[t, shared_gate_col]) * shared[t].  ``w_gate_up`` [E, 2F, W] (an expert's gate rows,
+    sigmoid(logits[t, shared_gate_col]) * shared[t] (``shared_gate_col`` negative: plus shared[t]).  ``w_gate_up`` [E, 2F, W] (an expert's gate rows,
     then its up rows), ``w_down`` [E, W, F], both of x's type.  The (token, expert) pairs are sorted by
     expert on the device into tiles of EXPERT_TILE_ROWS (or EXPERT_TILE_ROWS_LARGE) rows of one expert; a
     row's sums run over k in an order that its tile does not change, so a token's result does not depend
@@ -1270,6 +1383,8 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
         if tuple(shared.shape) != (t, w) or logits.shape[0] != t or logits.shape[1] <= shared_gate_col:
             raise KernelError(f"routed_experts: shared output {tuple(shared.shape)}, logits {tuple(logits.shape)}")
         sh, lg, row = _source_args(shared), _source_args(logits), logits.shape[1]
+        if shared_gate_col < 0:
+            shared_gate_col = -1
     else:
         sh = lg = (c_void_p(0), c_int(0), c_int(1), c_longlong(0))
         row = 0
@@ -1316,16 +1431,36 @@ def _cache_pages(kv_cache, page_elems: int, what: str) -> int:
 def attn_prepare(proj, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, q_norm_weight,
                  k_norm_weight, eps: float, freq, rotary_dim: int, positions: torch.Tensor, kv_cache,
                  slot_mapping, page_size: int, out_dtype, bias=None, norm_scope: str = "head",
-                 rotary_layout: str = "halves") -> torch.Tensor:
+                 rotary_layout: str = "halves", conv_weight=None, conv_state=None, step=None) -> torch.Tensor:
     """From each token's projection row [q heads | k heads | v heads | anything else] (plus ``bias``,
     float32 over q, k and v, when given): RMS norm of q and k (when a weight is given; ``norm_scope``
     "head": per head, weights of head_dim elements; "projection": over all of q's (k's) heads at once,
     weights of that many elements), rotation of the first ``rotary_dim`` elements of each head by the
     token's position (``rotary_layout`` "halves": element i with i + rotary_dim / 2, "pairs": element 2i
     with 2i + 1; angle = position * freq[i], float32), q [T, Hq, D] returned, k and v to the token's slot
-    of the paged cache (a page: keys [Hkv, page_size, D], then values [Hkv, page_size, Dv])."""
+    of the paged cache (a page: keys [Hkv, page_size, D], then values [Hkv, page_size, Dv]).
+    ``conv_weight`` (float32 [q + k + v channels, taps], the last tap the current token's): each channel
+    of q, k and v first passes a causal convolution over its sequence's tokens, before norm and rotation;
+    the inputs before the step's first token come from ``conv_state`` (float32 [slots, (taps - 1) *
+    channels], rows ``step.state_slots``, oldest input first), which is moved on by the step's tokens."""
     t, width = proj.shape
     need = num_heads * head_dim + num_kv_heads * (head_dim + v_head_dim)
+    conv_args = [c_void_p(0), c_int(0), c_void_p(0), c_longlong(0), c_longlong(0), c_void_p(0), c_void_p(0),
+                 c_void_p(0), c_int(0)]
+    if conv_weight is not None:
+        _need(conv_weight, "conv_weight", torch.float32, 2)
+        taps = conv_weight.shape[1]
+        if conv_weight.shape[0] != need or step is None:
+            raise KernelError(f"attn_prepare: convolution weights of shape {tuple(conv_weight.shape)} for {need} "
+                              f"channels (and the step's sequences are needed)")
+        if taps > 1:
+            _need(conv_state, "conv_state", torch.float32, 2)
+            if conv_state.shape[1] != (taps - 1) * need:
+                raise KernelError(f"attn_prepare: state rows of {conv_state.shape[1]} floats for {taps} taps of "
+                                  f"{need} channels")
+        conv_args = [_ptr(conv_weight), c_int(taps), _ptr(conv_state if taps > 1 else None),
+                     c_longlong(conv_state.shape[1] if taps > 1 else 0), c_longlong(0), _ptr(step.token_seq),
+                     _ptr(step.cu_q_lens), _ptr(step.state_slots), c_int(step.num_seqs)]
     if width < need:
         raise KernelError(f"attn_prepare: rows of {width} elements, q, k and v need {need}")
     if norm_scope not in ("head", "projection") or rotary_layout not in ("halves", "pairs"):
@@ -1352,15 +1487,16 @@ def attn_prepare(proj, num_heads: int, num_kv_heads: int, head_dim: int, v_head_
         _need(slot_mapping, "slot_mapping", torch.int32, 1)
         num_pages = _cache_pages(kv_cache, num_kv_heads * page_size * (head_dim + v_head_dim), "attn_prepare")
     q = torch.empty(t, num_heads, head_dim, dtype=out_dtype, device=proj.device)
-    if bias is not None or whole or rotary_layout == "pairs":
+    if bias is not None or whole or rotary_layout == "pairs" or conv_weight is not None:
         # a block per token: it sees all heads of the row at once
         st = _lib("masked_attention").dib_attn_prepare_row(
             *_source_args(proj), c_longlong(width), _ptr(bias), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight),
             _ptr(k_norm_weight), c_int(1 if whole else 0), c_float(eps), _ptr(freq),
             c_int(rotary_dim if freq is not None else 0), c_int(1 if rotary_layout == "pairs" else 0), _ptr(positions),
             _ptr(slot_mapping), c_int(t), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
-            c_int(page_size), c_longlong(num_pages), c_int(_DT[out_dtype]), _stream())
-        _check(st, "attn_prepare(row)", f"heads {num_heads}/{num_kv_heads} of {head_dim}/{v_head_dim}")
+            c_int(page_size), c_longlong(num_pages), c_int(_DT[out_dtype]), *conv_args, _stream())
+        _check(st, "attn_prepare(row)", f"heads {num_heads}/{num_kv_heads} of {head_dim}/{v_head_dim}",
+               kernels=2 if conv_weight is not None and conv_weight.shape[1] > 1 else 1)
         return q
     st = _lib("masked_attention").dib_attn_prepare(
         *_source_args(proj), c_longlong(width), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight),
@@ -1444,13 +1580,18 @@ HEADS_LINEAR_LIBRARY_ROWS = int(__import__("os").environ.get("DIB200_HEADS_LINEA
 
 def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, num_kv_heads: int,
                      v_head_dim: int, page_size: int, mask: str = "causal", mask_size=None, sink=None,
-                     gate=None, gate_col: int = 0, values_in_keys: bool = False, keep_first: int = 0) -> torch.Tensor:
+                     gate=None, gate_col: int = 0, values_in_keys: bool = False, keep_first: int = 0,
+                     softcap=None) -> torch.Tensor:
     """[T, Hq, Dv]: softmax attention of every token of the step over the keys of its sequence in the
     paged cache that ``mask`` lets it see (a query at position p: "causal" 0 .. p; "window" p - size + 1
     .. p, and with ``keep_first`` also the keys 0 .. keep_first - 1; "chunk" floor(p / size) * size .. p).  ``sink`` float32 [Hq]: the denominator also holds
     exp(sink[h]) as one more term that brings nothing into the output and is taken as it is.  ``gate`` [T, >= gate_col + Hq * Dv] (a tensor or split
     sums): the output is multiplied by sigmoid(gate[t, gate_col + h * Dv + d]).  ``values_in_keys``: the
-    cache holds keys only and a key's first Dv elements are its value."""
+    cache holds keys only and a key's first Dv elements are its value.  ``softcap`` c: a score (after the
+    scale) becomes c * tanh(score / c) before the softmax."""
+    cap = 0.0 if softcap is None else float(softcap)
+    if cap < 0.0:
+        raise KernelError("masked_attention: a soft cap is positive")
     _need(q, "q", None, 3)
     _need(kv_cache, "kv_cache", q.dtype)
     t, hq, dk = q.shape
@@ -1476,6 +1617,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
     _need(meta.positions, "positions", torch.int32, 1)
     out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
     if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and not values_in_keys and dk == v_head_dim and not keep \
+            and not cap \
             and getattr(meta, "q_lens", None) is not None and getattr(meta, "num_decode", None) is not None:
         # keys and values of one size that the tensor-core kernels of ``attention_bf16`` take: the
         # split-KV decode kernels for the step's one-token sequences, the tcgen05 kernel (heads of
@@ -1532,7 +1674,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                     c_int(hq), c_int(num_kv_heads), c_int(dk), c_int(v_head_dim), c_int(dv_stored),
                     c_int(page_size), c_float(scale), c_int(kind), c_int(size), c_int(keep), *gate_args,
                     c_longlong(gate_row), c_longlong(gate_col), c_int(form_rows), _ptr(part_o), _ptr(part_ml),
-                    c_int(MASKED_DECODE_CHUNK_TILES), c_int(max_chunks), c_int(n_dec), _stream())
+                    c_int(MASKED_DECODE_CHUNK_TILES), c_int(max_chunks), c_int(n_dec), c_float(cap), _stream())
                 _check(st, "masked_attention(tensor cores)", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}",
                        kernels=2 if part_o is not None else 1)
             return out
@@ -1540,6 +1682,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
         _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(num_kv_heads), c_int(dk),
         c_int(v_head_dim), c_int(dv_stored), c_int(page_size), c_float(scale), c_int(kind), c_int(size), c_int(keep),
-        _ptr(sink), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(_dt(q, "q")), _stream())
+        _ptr(sink), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(_dt(q, "q")), c_float(cap),
+        _stream())
     _check(st, "masked_attention", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}")
     return out

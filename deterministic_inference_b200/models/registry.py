@@ -15,6 +15,7 @@ from pathlib import Path
 
 import torch
 
+from ..config.bovitar_config import BovitarConfig
 from ..config.gamilorn_config import GamilornConfig
 from ..config.kipezen_config import KipezenConfig
 from ..config.model_config import Qwen3Config
@@ -37,6 +38,7 @@ register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Gamilorn", GamilornConfig)
 register_architecture("Zatirax", ZatiraxConfig)
 register_architecture("Kipezen", KipezenConfig)
+register_architecture("Bovitar", BovitarConfig)
 
 
 def config_from_dir(model_dir):

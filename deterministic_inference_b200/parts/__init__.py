@@ -8,4 +8,5 @@ from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, 
 from .spec import (CompositeSpec, LayerSpec, ModelPlan, PagedKVSpec, PartSpec, ScheduleEntry, StateSpec,
                    TensorSpec)
 from . import (attention, block, delta_rule, embedding, feed_forward, gated_delta_rule, gated_linear_recurrence,
-               latent_attention, masked_attention, norm, parallel, position, routed_experts, sigmoid_attention)  # noqa: F401  (register the kinds)
+               latent_attention, masked_attention, norm, parallel, position, routed_experts, sigmoid_attention,
+               state_space)  # noqa: F401  (register the kinds)

@@ -109,13 +109,15 @@ class RowVectors(Part):
 
 @register_head("linear_head")
 class LinearHead(Head):
-    """logits = rows @ W^T in float32.  ``name`` None: W is the embedding's table."""
+    """logits = rows @ W^T in float32, times ``scale`` (when it is not 1).  ``name`` None: W is the
+    embedding's table."""
 
     def __init__(self, ctx, name: Optional[str], vocab_size: int, hidden_size: int,
-                 softcap: Optional[float] = None):
+                 softcap: Optional[float] = None, scale: float = 1.0):
         self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
         # softcap c: logits <- c * tanh(logits / c)
         self.softcap = None if softcap is None else float(softcap)
+        self.scale = float(scale)
         self.tied = name is None
         self.weight = None
 
@@ -130,4 +132,6 @@ class LinearHead(Head):
     def forward(self, rows):
         # logits leave as a plain tensor (the product may come as split-k partials)
         logits = ops.as_tensor(ops.linear(rows, self.weight, out_dtype=torch.float32))
+        if self.scale != 1.0:
+            logits = ops.scale_(logits, self.scale)
         return logits if self.softcap is None else ops.softcap_(logits, self.softcap)

@@ -176,14 +176,35 @@ class CompositeSpec:
 
 def flatten_cache_specs(cache_specs: dict) -> dict:
     """cache id -> need, with every ``CompositeSpec`` replaced by its members under the ids
-    ``(cache id, member index)``; members that keep nothing are left out."""
+    ``(cache id, member index)``; members that keep nothing are left out.  A member may be a
+    composite itself (a mixer that keeps pages and a state row inside a pair of mixers): its
+    members get the ids ``((cache id, member index), member index)``."""
     flat = {}
-    for cid in sorted(cache_specs):
-        spec = cache_specs[cid]
+
+    def walk(cid, spec):
         if isinstance(spec, CompositeSpec):
             for mi, m in enumerate(spec.members):
                 if m is not None:
-                    flat[(cid, mi)] = m
+                    walk((cid, mi), m)
         else:
             flat[cid] = spec
+
+    for cid in sorted(cache_specs):
+        walk(cid, cache_specs[cid])
     return flat
+
+
+def composite_cache_ids(cache_specs: dict) -> dict:
+    """id of every composite cache (nested ones under their ``(cache id, member index)`` ids) -> its
+    number of members."""
+    out = {}
+
+    def walk(cid, spec):
+        if isinstance(spec, CompositeSpec):
+            out[cid] = len(spec.members)
+            for mi, m in enumerate(spec.members):
+                walk((cid, mi), m)
+
+    for cid, spec in cache_specs.items():
+        walk(cid, spec)
+    return out

@@ -230,6 +230,11 @@ def xielu(z, alpha_p, alpha_n, out_dtype):
     return torch.where(z > 0, pos, neg).to(out_dtype)
 
 
+def scale_(x, a):
+    x.mul_(a)
+    return x
+
+
 def softcap_(logits, cap):
     logits.copy_(cap * torch.tanh(logits / cap))
     return logits
@@ -365,13 +370,19 @@ def _rotate_pairs(x, positions, freq, rot):
 
 def attn_prepare(proj, num_heads, num_kv_heads, head_dim, v_head_dim, q_norm_weight, k_norm_weight, eps, freq,
                  rotary_dim, positions, kv_cache, slot_mapping, page_size, out_dtype, bias=None, norm_scope="head",
-                 rotary_layout="halves"):
+                 rotary_layout="halves", conv_weight=None, conv_state=None, step=None):
     t = proj.shape[0]
     nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_head_dim
     x = _plain(proj)[:, :nq + nk + nv]
     if bias is not None:
         x = x + bias
-    x = x.to(out_dtype).float()
+    if conv_weight is not None:
+        taps = conv_weight.shape[1]
+        tail = conv_state.view(conv_state.shape[0], taps - 1, nq + nk + nv) if taps > 1 \
+            else torch.zeros(int(step.state_slots.max()) + 1, 0, nq + nk + nv)
+        x = _conv_with_tail(x.contiguous(), conv_weight, tail, step.cu_q_lens.tolist(), step.state_slots.tolist())
+    else:
+        x = x.to(out_dtype).float()
     q, k = x[:, :nq], x[:, nq:nq + nk]
     if norm_scope == "head":
         q, k = q.reshape(t, num_heads, head_dim), k.reshape(t, num_kv_heads, head_dim)
@@ -420,7 +431,7 @@ def heads_linear(x, weight, out):
 
 
 def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_size, mask="causal", mask_size=None,
-                     sink=None, gate=None, gate_col=0, values_in_keys=False, keep_first=0):
+                     sink=None, gate=None, gate_col=0, values_in_keys=False, keep_first=0, softcap=None):
     t, hq, dk = q.shape
     flat = kv_cache.view(kv_cache.shape[0], -1)
     keys_of = flat[:, :num_kv_heads * page_size * dk].view(-1, num_kv_heads, page_size, dk)
@@ -441,6 +452,8 @@ def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_si
             k = keys_of[pages, h // group, js % page_size].float()
             v = k[:, :v_head_dim] if values_in_keys else values_of[pages, h // group, js % page_size].float()
             s = (k @ q[i, h].float()) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             if sink is not None:
                 s = torch.cat([s, sink[h].float().reshape(1)])
             w = torch.softmax(s, dim=0)[:js.shape[0]]
@@ -532,19 +545,50 @@ def gated_linear_recurrence(proj, bias, conv_weight, conv_bias, gates, gate_bias
     return out.to(out_dtype)
 
 
-def route_experts(logits, correction, num_experts, top, group_count, group_keep, scale, eps):
+def state_space(proj, conv_weight, conv_bias, a_log, dt_bias, d_skip, norm_weight, state, step, num_heads,
+                head_dim, state_dim, groups, norm_groups, taps, norm_eps, out_dtype):
+    x_all = _plain(proj)
+    t, h, p, n, g = x_all.shape[0], num_heads, head_dim, state_dim, groups
+    inner, chan = h * p, h * p + 2 * g * n
+    cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
+    n_state = h * n * p
+    tail = state[:, n_state:].view(state.shape[0], taps - 1, chan)
+    z = x_all[:, :inner]
+    c = _conv_with_tail(x_all[:, inner:inner + chan], conv_weight, tail, cu, slots, conv_bias)
+    c = c * torch.sigmoid(c)
+    x = c[:, :inner].reshape(t, h, p)
+    pick = torch.arange(h) // (h // g)
+    bm = c[:, inner:inner + g * n].reshape(t, g, n)[:, pick]
+    cm = c[:, inner + g * n:].reshape(t, g, n)[:, pick]
+    dt = torch.nn.functional.softplus(x_all[:, inner + chan:inner + chan + h] + dt_bias)
+    decay = torch.exp(-torch.exp(a_log) * dt)
+    y = torch.zeros(t, h, p)
+    for b in range(len(slots)):
+        s = state[slots[b], :n_state].view(h, n, p).clone() if slots[b] else torch.zeros(h, n, p)
+        for i in range(cu[b], cu[b + 1]):
+            s = decay[i][:, None, None] * s + dt[i][:, None, None] * bm[i][:, :, None] * x[i][:, None, :]
+            y[i] = torch.einsum("hnp,hn->hp", s, cm[i]) + d_skip[:, None] * x[i]
+        if slots[b]:
+            state[slots[b], :n_state] = s.reshape(-1)
+    u = (y.reshape(t, inner) * (z * torch.sigmoid(z))).reshape(t, norm_groups, inner // norm_groups)
+    u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + norm_eps)
+    return (u.reshape(t, inner) * norm_weight).to(out_dtype)
+
+
+def route_experts(logits, correction, num_experts, top, group_count, group_keep, scale, eps, score="sigmoid",
+                  group_top=2, normalize=True):
     z = _plain(logits)[:, :num_experts]
-    s = torch.sigmoid(z)
+    s = torch.softmax(z, dim=-1) if score == "softmax" else torch.sigmoid(z)
     choice = s + correction
     per = num_experts // group_count
     by_group = choice.view(-1, group_count, per)
-    group_score = by_group.topk(min(2, per), dim=-1).values.sum(-1)
+    group_score = by_group.topk(min(group_top, per), dim=-1).values.sum(-1)
     best = group_score.topk(group_keep, dim=-1).indices
     allowed = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, best, True)
     masked = by_group.masked_fill(~allowed[:, :, None], float("-inf")).reshape(-1, num_experts)
     ids = masked.topk(top, dim=-1).indices
     w = s.gather(1, ids)
-    w = w / (w.sum(-1, keepdim=True) + eps) * scale
+    w = w / (w.sum(-1, keepdim=True) + eps) * scale if normalize else w * scale
     return ids.to(torch.int32), w
 
 
@@ -558,12 +602,14 @@ def routed_experts(x, ids, weights, w_gate_up, w_down, shared, logits, shared_ga
             gu = w_gate_up[e].float() @ x[i].float()
             hdn = (gu[:f] * torch.sigmoid(gu[:f]) * gu[f:]).to(x.dtype).float()
             out[i] += weights[i, j] * (w_down[e].float() @ hdn)
-    if shared is not None:
+    if shared is not None and shared_gate_col < 0:
+        out = out + _plain(shared)
+    elif shared is not None:
         out = out + torch.sigmoid(_plain(logits)[:, shared_gate_col:shared_gate_col + 1]) * _plain(shared)
     return out
 
 
-ALL = ("stream_read", "gated_delta_rule", "gated_linear_recurrence", "route_experts", "routed_experts",
+ALL = ("state_space", "scale_", "stream_read", "gated_delta_rule", "gated_linear_recurrence", "route_experts", "routed_experts",
        "embedding_scaled", "stream_add_", "limited_gate", "attn_prepare", "latent_prepare", "heads_linear",
        "masked_attention", "embedding_positions", "stream_rms_norm", "xielu", "softcap_", "qkv_bias_cache", "sigmoid_attention",
        "delta_rule", "patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
