@@ -252,8 +252,13 @@ def expert(h, w, p, rnd=_keep):
     return rnd(a @ w[p + "down"].T)
 
 
-def moe_feed_forward(h, w, p, c, rnd=_keep, follow=None):
-    ids, weights, _ = route(h, w, p, c["router"], follow)
+def moe_feed_forward(h, w, p, c, rnd=_keep, follow=None, gaps=None):
+    """``gaps`` (a list, with ``follow``): receives, per token, how far the followed choice's worst
+    choice score lies below the rule's own worst chosen one (0 where they agree)."""
+    ids, weights, masked = route(h, w, p, c["router"], follow)
+    if gaps is not None and follow is not None:
+        own = masked.topk(ids.shape[1], dim=-1).values.min(-1).values
+        gaps.append(own - masked.gather(1, ids).min(-1).values)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(ids.shape[1]):
@@ -265,9 +270,10 @@ def moe_feed_forward(h, w, p, c, rnd=_keep, follow=None):
 
 # ---- the model ------------------------------------------------------------------------------------
 
-def forward(cfg, w, tokens, rnd=_keep, layers_out=None, follow=None):
+def forward(cfg, w, tokens, rnd=_keep, layers_out=None, follow=None, gaps=None):
     """Logits [n, vocab] of one sequence.  ``layers_out``: a list that receives the residual stream
-    after every layer run.  ``follow``: {layer run: chosen experts [n, top]}."""
+    after every layer run.  ``follow``: {layer run: chosen experts [n, top]}; ``gaps``: see
+    ``moe_feed_forward``."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -282,7 +288,7 @@ def forward(cfg, w, tokens, rnd=_keep, layers_out=None, follow=None):
         if layer.get("mlp") is not None:
             h = rnd(rms_norm(x, w[p + "norm2"], eps))
             x = x + moe_feed_forward(h, w, p + "mlp.", layer["mlp"], rnd,
-                                     None if follow is None else follow.get(i))
+                                     None if follow is None else follow.get(i), gaps)
         if layers_out is not None:
             layers_out.append(x.clone())
     x = rnd(rms_norm(x, w["final.norm"], eps))
