@@ -364,6 +364,45 @@ def kipezen_like(q, layers: int, window: int, keep: int, taps: int, experts: int
         "norm": {"eps": 1e-6}, "layers": [delta if i % 2 == 0 else par for i in range(layers)]})
 
 
+BOVITAR_SIZES = {
+    # name -> the Bovitar sizes that go with the Qwen3 preset of DESIGN_SIZES[name]: the delta and the attention
+    # heads are Qwen3's, the state-space branch is as wide as the model in heads of 64 with a state of 128, and
+    # the experts are Kipezen's
+    "0_6b": dict(taps=4, softcap=30.0, state=128, ssm_groups=1, norm_groups=1, experts=16, top=2, expert_ff=768,
+                 shared_ff=1536, groups=(4, 2)),
+    "8b": dict(taps=4, softcap=30.0, state=128, ssm_groups=8, norm_groups=8, experts=32, top=4, expert_ff=1536,
+               shared_ff=6144, groups=(8, 4)),
+}
+
+
+def bovitar_like(q, layers: int, taps: int, softcap: float, state: int, ssm_groups: int, norm_groups: int,
+                 experts: int, top: int, expert_ff: int, shared_ff: int, groups: tuple):
+    """A Bovitar configuration with the layer sizes of the Qwen3 configuration ``q``: delta layers and
+    parallel layers (attention beside the state-space branch) in turn, every one with routed experts; the
+    second half of the layers runs with the weights of the first half."""
+    from deterministic_inference_b200.config.bovitar_config import BovitarConfig
+    d = q.head_dim
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups[0], "keep": groups[1]}}}
+    delta = {"type": "delta", "mlp": mlp,
+             "mixer": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads, "dim": d, "vdim": d,
+                       "conv": taps}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads, "dim": d, "vdim": d,
+                              "conv": taps, "scale": d ** -0.5, "softcap": softcap,
+                              "rot": {"base": 500000.0, "dims": d // 2,
+                                      "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+                     "right": {"heads": q.hidden_size // 64, "vdim": 64, "state": state, "groups": ssm_groups,
+                               "norm_groups": norm_groups, "conv": taps}}}
+    own = max(2, layers // 2)
+    entries = [dict(delta if i % 2 == 0 else par) for i in range(layers)]
+    for i in range(own, layers):
+        entries[i] = dict(entries[i], weights_of=i - own) if (i - own) % 2 == i % 2 else entries[i]
+    return BovitarConfig.from_dict({
+        "architecture": "Bovitar", "vocab": q.vocab_size, "width": q.hidden_size, "max_positions": 8192,
+        "norm": {"eps": 1e-6}, "logit_scale": 0.5, "layers": entries})
+
+
 def design_arm(a) -> int:
     """``--design zatirax``: the same for the Zatirax design; ``--design kipezen``: for the Kipezen design,
     beside Gamilorn (the closest design) instead of Qwen3.  ``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
@@ -733,6 +772,119 @@ def design_arm(a) -> int:
                     cache.release_slot(sl)
         return rows
 
+    def bovitar_kernel_rows(eng_b, eng_k, bcfg, kcfg):
+        """Bovitar's kernels and the like kernels of Kipezen (the closest design: a gated delta rule, softmax
+        attention beside a recurrent unit, routed experts, a float32 stream) on one layer's shapes: a prompt of
+        ``n_prompt`` tokens, and a decode step of 8 requests with ``ctx`` cached tokens."""
+        rows = {}
+        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        par = bcfg.layers[1]["mixer"]
+        left, right, mlp = par["left"], par["right"], bcfg.layers[0]["mlp"]
+        hq, hkv, d, w = left["heads"], left["kv_heads"], left["dim"], bcfg.width
+        n_exp, top = mlp["router"]["experts"], mlp["router"]["top"]
+        k_left, k_right = kcfg.layers[1]["mixer"]["left"], kcfg.layers[1]["mixer"]["right"]
+        win, keep = k_left["mask"]["size"], k_left["mask"]["keep_first"]
+        sh, sp, sn, sg = right["heads"], right["vdim"], right["state"], right["groups"]
+        inner, chan = sh * sp, sh * sp + 2 * sg * sn
+        bf = torch.bfloat16
+
+        def row(name, ms, nbytes, flops):
+            floor = max(nbytes / hbm, flops / tf) * 1e3
+            rows[name] = {"ms": round(ms, 4), "roofline_ms": round(floor, 4), "of_roofline": round(floor / ms, 4)}
+
+        for what, batch, q_len, before in (("prompt", 1, n_prompt, 0), ("decode_b8", 8, 1, ctx)):
+            t = batch * q_len
+            span = range(before, before + q_len)
+            for eng, mine in ((eng_b, True), (eng_k, False)):
+                runner, cache = eng.runner, eng.cache
+                slots = [cache.allocate_slot() for _ in range(batch)]
+                if before:
+                    for sl in slots:
+                        runner.step([SequenceInput(sl, prompt_of(1000, before), 0, [])])
+                entries = [SequenceInput(sl, [1] * q_len, before, []) for sl in slots]
+                for e_ in entries:
+                    cache.allocate(e_.slot, before + q_len)
+                cache.reset_fresh_state()
+                step = build_step_batch(entries, cache, dev)
+                q = torch.randn(t, hq, d, device=dev).to(bf)
+                x = torch.randn(t, w, device=dev).to(bf)
+                stream = torch.randn(t, w, device=dev)
+                one_w = torch.ones(w, device=dev)
+                blocks = runner.model.blocks
+                pview = cache.view(1, step)
+                ff = blocks[0].feed_forward
+                logits = torch.randn(t, ff.w_router.shape[0], device=dev)
+                proj = torch.randn(t, (hq + 2 * hkv) * d, device=dev)
+                if mine:
+                    att, ssm = blocks[1].mixer.branches[0], blocks[1].mixer.branches[1]
+                    kv, tail, sstate = pview.members[0].members[0], pview.members[0].members[1].state, pview.members[1].state
+                    keys = batch * sum(p + 1 for p in span)
+                    held = before + q_len
+                    row(f"{what}: attention, causal, soft-capped scores", timed(lambda: ops.masked_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, hkv, d, kv.page_size, "causal", None,
+                        softcap=left["softcap"])),
+                        2 * (2 * t * hq * d + batch * hkv * 2 * d * held), 4 * keys * hq * d)
+                    row(f"{what}: q/k/v convolutions + norm over the projection + rotation + cache write", timed(
+                        lambda: ops.attn_prepare(proj, hq, hkv, d, d, att.q_norm, att.k_norm, 1e-6, att.freq,
+                                                 att.rotary_dim, step.positions, kv.kv, kv.slot_mapping, kv.page_size, bf,
+                                                 norm_scope="projection", rotary_layout="halves", conv_weight=att.conv,
+                                                 conv_state=tail, step=step)),
+                        proj.numel() * 6 + batch * tail.shape[1] * 8, 0)
+                    sproj = torch.randn(t, ssm.w_in.shape[0], device=dev)
+                    row(f"{what}: state-space branch (convolution, recurrence, gated norm)", timed(lambda: ops.state_space(
+                        sproj, ssm.conv, ssm.conv_bias, ssm.a_log, ssm.dt_bias, ssm.d_skip, ssm.norm_weight, sstate, step,
+                        sh, sp, sn, sg, right["norm_groups"], right["conv"], 1e-6, bf)),
+                        batch * sh * sn * sp * 4 * 2 + t * (sproj.shape[1] * 4 + chan * 8 + inner * 10),
+                        5 * t * sh * sn * sp)
+                    row(f"{what}: two normed branches + add + norm of the float32 stream", timed(
+                        lambda: ops.stream_rms_norm(stream, one_w, 1e-6, bf, add=ops.WeightedSum(
+                            [(0.5, ops.NormedTerm(x, one_w, 1e-6)), (0.5, ops.NormedTerm(x, one_w, 1e-6))]))),
+                        t * w * (4 + 4 + 2 + 2 + 2), 0)
+                    row(f"{what}: softmax router", timed(lambda: ops.route_experts(
+                        logits, ff.correction, n_exp, top, ff.group_count, ff.group_keep, 2.5, 0.0, score="softmax",
+                        group_top=1, normalize=False)), t * (logits.shape[1] * 4 + top * 8), 0)
+                else:
+                    att, glr = blocks[1].mixer.branches[0], blocks[1].mixer.branches[1]
+                    kv, rstate = pview.members[0], pview.members[1].state
+                    keys = batch * sum(min(p + 1, win + keep) for p in span)
+                    held = min(before + q_len, win + keep)
+                    row(f"{what}: kipezen attention, window + kept first keys", timed(lambda: ops.masked_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, hkv, d, kv.page_size, "window", win, keep_first=keep)),
+                        2 * (2 * t * hq * d + batch * hkv * 2 * d * held), 4 * keys * hq * d)
+                    row(f"{what}: kipezen q/k/v bias + norm over the projection + pair rotation + cache write", timed(
+                        lambda: ops.attn_prepare(proj, hq, hkv, d, d, att.q_norm, att.k_norm, 1e-6, att.freq,
+                                                 att.rotary_dim, step.positions, kv.kv, kv.slot_mapping, kv.page_size, bf,
+                                                 bias=att.b_in, norm_scope="projection", rotary_layout="pairs")),
+                        proj.numel() * 6, 0)
+                    c, per = k_right["width"], k_right["width"] // k_right["blocks"]
+                    rproj = torch.randn(t, 2 * c, device=dev)
+                    row(f"{what}: kipezen gated linear recurrence (convolution, gates, scan)", timed(
+                        lambda: ops.gated_linear_recurrence(rproj, glr.b_in, glr.conv, glr.conv_bias, glr.gates,
+                                                            glr.gate_bias, glr.neg_rate, rstate, step, c, k_right["blocks"],
+                                                            k_right["conv"], bf)),
+                        t * c * (8 + 2) + batch * k_right["conv"] * c * 8 + 2 * c * per * 4, 4 * t * c * per)
+                    dl = kcfg.layers[0]["mixer"]
+                    delta, dview = blocks[0].mixer, cache.view(0, step)
+                    h, g, e = dl["heads"], dl["kv_heads"], dl["vdim"]
+                    dproj = torch.randn(t, delta.w_in.shape[0], device=dev)
+                    row(f"{what}: kipezen gated delta rule (convolutions, recurrence, output; the same kernels serve both designs)",
+                        timed(lambda: ops.gated_delta_rule(
+                            dproj, delta.conv, delta.a_log, delta.dt_bias, delta.norm_weight, dview.state, step, h, g, d, e,
+                            dl["conv"], 1e-6, 1e-6, bf)),
+                        batch * h * d * e * 4 * 2 + t * (dproj.shape[1] * 4 + h * e * 2), 8 * t * h * d * e)
+                    row(f"{what}: kipezen post norm + add into the float32 stream + read", timed(lambda: ops.stream_read(
+                        stream, ops.NormedTerm(x, one_w, 1e-6), bf)), t * w * (4 + 4 + 2 + 2), 0)
+                    row(f"{what}: kipezen sigmoid router", timed(lambda: ops.route_experts(
+                        logits, ff.correction, n_exp, top, ff.group_count, ff.group_keep, 2.5, 1e-20)),
+                        t * (logits.shape[1] * 4 + top * 8), 0)
+                eff, sff = mlp["expert"]["ff"], mlp["shared"]["ff"]
+                row(f"{what}: {'' if mine else 'kipezen '}feed-forward (router, shared expert, routed experts)",
+                    timed(lambda: ff.forward(x)),
+                    (min(n_exp, t * top) * eff + sff) * 3 * w * 2 + t * w * 6, 2 * t * 3 * (top * eff + sff) * w)
+                for sl in slots:
+                    cache.release_slot(sl)
+        return rows
+
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
@@ -748,6 +900,11 @@ def design_arm(a) -> int:
             beside, bcfg = "gamilorn", gamilorn_like(qcfg, n_layers, **extra)
             extra = KIPEZEN_SIZES[name]
             gcfg = kipezen_like(qcfg, n_layers, **extra)
+        elif a.design == "bovitar":
+            # beside Kipezen, the closest design, at the same layer sizes
+            beside, bcfg = "kipezen", kipezen_like(qcfg, n_layers, **KIPEZEN_SIZES[name])
+            extra = BOVITAR_SIZES[name]
+            gcfg = bovitar_like(qcfg, n_layers, **extra)
         else:
             gcfg = gamilorn_like(qcfg, n_layers, **extra)
         out = {"layers": n_layers, "width": qcfg.hidden_size, "heads": f"{qcfg.num_attention_heads}/{qcfg.num_key_value_heads} x {qcfg.head_dim}",
@@ -763,14 +920,15 @@ def design_arm(a) -> int:
                 r[f"decode_b{b}_ms"] = round(dms, 4)
                 r[f"decode_b{b}_tok_s"] = round(b / (dms / 1e3))
             out[label + "_result"] = r
-        rows_of = {"zatirax": zatirax_kernel_rows, "kipezen": kipezen_kernel_rows}.get(a.design, kernel_rows)
+        rows_of = {"zatirax": zatirax_kernel_rows, "kipezen": kipezen_kernel_rows,
+                   "bovitar": bovitar_kernel_rows}.get(a.design, kernel_rows)
         out["kernels"] = rows_of(engines[a.design], engines[beside], gcfg, bcfg)
         sizes[name] = out
         del engines
         import gc
         gc.collect()
         torch.cuda.empty_cache()
-    beside = "gamilorn" if a.design == "kipezen" else "qwen3"
+    beside = {"kipezen": "gamilorn", "bovitar": "kipezen"}.get(a.design, "qwen3")
     print(json.dumps({"metric": f"{a.design} beside {beside} at equal layer sizes (bf16, 1 B200)", "impl": "ours",
                       "dtype": "bf16", "data": "synthetic, random weights", "n_gpus": 1,
                       "prompt_tokens": n_prompt, "decode_context": ctx, "decode_steps": a.point_steps,
@@ -805,8 +963,8 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); the numbers of such a run are not a result")
-    ap.add_argument("--design", default=None, choices=["gamilorn", "zatirax", "kipezen"],
-                    help="measure this design beside Qwen3 (kipezen: beside Gamilorn) at equal layer sizes instead of the default "
+    ap.add_argument("--design", default=None, choices=["gamilorn", "zatirax", "kipezen", "bovitar"],
+                    help="measure this design beside Qwen3 (kipezen: beside Gamilorn; bovitar: beside Kipezen) at equal layer sizes instead of the default "
                          "workload (prints a line of its own)")
     ap.add_argument("--design-sizes", default="0_6b,8b", help=f"of {sorted(DESIGN_SIZES)}")
     ap.add_argument("--design-layers", type=int, default=4)

@@ -252,13 +252,31 @@ def expert(h, w, p, rnd=_keep):
     return rnd(a @ w[p + "down"].T)
 
 
+def route_gap(h, w, p, r, ids):
+    """How far a given choice ``ids`` [n, top] is from the rule's own, per token, in units of the choice
+    scores: the larger of (a) how far the worst group it uses lies below the rule's worst kept group and
+    (b) how far its worst expert lies below the worst expert the rule would choose among the groups
+    that the rule keeps or the choice uses.  0 where the choice is the rule's."""
+    experts, top = r["experts"], r["top"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    n, per = h.shape[0], experts // groups["count"]
+    choice = torch.softmax(h @ w[p + "router"].T, dim=-1) + w[p + "correction"]
+    gscore = choice.reshape(n, groups["count"], per).max(-1).values
+    kept_worst = gscore.topk(groups["keep"], dim=-1).values.min(-1).values
+    used_worst = gscore.gather(1, ids // per).min(-1).values
+    allowed = torch.zeros(n, groups["count"], dtype=torch.bool)
+    allowed.scatter_(1, gscore.topk(groups["keep"], dim=-1).indices, True)
+    allowed.scatter_(1, ids // per, True)
+    masked = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
+    own = masked.topk(top, dim=-1).values.min(-1).values
+    return torch.maximum(kept_worst - used_worst, own - choice.gather(1, ids).min(-1).values).clamp(min=0.0)
+
+
 def moe_feed_forward(h, w, p, c, rnd=_keep, follow=None, gaps=None):
-    """``gaps`` (a list, with ``follow``): receives, per token, how far the followed choice's worst
-    choice score lies below the rule's own worst chosen one (0 where they agree)."""
-    ids, weights, masked = route(h, w, p, c["router"], follow)
+    """``gaps`` (a list, with ``follow``): receives ``route_gap`` of the followed choice."""
+    ids, weights, _ = route(h, w, p, c["router"], follow)
     if gaps is not None and follow is not None:
-        own = masked.topk(ids.shape[1], dim=-1).values.min(-1).values
-        gaps.append(own - masked.gather(1, ids).min(-1).values)
+        gaps.append(route_gap(h, w, p, c["router"], ids))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(ids.shape[1]):
