@@ -56,20 +56,23 @@ ssm_prepare_kernel(Source proj, long long row_width, const float* __restrict__ c
     }
 }
 
-// grid (B, H, ceil(P / 8)), 128 threads: 8 columns of the head's state, a column's N rows over 16
-// lanes (row n on lane n % 16, so MAXR = ceil(N / 16) rows a lane, kept in registers).  The
-// sequence's tokens are walked in chunks of CHUNK tokens whose vectors (B and C of the head's
-// group, the 8 x of the block's columns, dt and the decay) are staged in shared memory by
-// cp.async, one chunk ahead of the arithmetic.  A column's read-out adds a lane's rows in
-// ascending order and then the 16 lanes by a butterfly: the order depends on N alone.
-template <int MAXR, int CHUNK>
-__global__ void __launch_bounds__(128)
+// grid (B, H, ceil(P / COLS)), COLS * 16 threads: COLS columns of the head's state, a column's N rows
+// over 16 lanes (row n on lane n % 16, so MAXR = ceil(N / 16) rows a lane, kept in registers).  The
+// sequence's tokens are walked in chunks of CHUNK tokens whose vectors (B and C of the head's group,
+// the x of the block's columns, dt and the decay) are staged in shared memory by cp.async (16 bytes
+// at a time where the sizes allow), one chunk ahead of the arithmetic.  A lane adds its rows'
+// share of a column's read-out in ascending order and leaves it in shared memory; once the chunk
+// is through, a thread per (token, column) adds the 16 lanes' shares in lane order: the order
+// depends on N alone, not on COLS, the chunk or the step.
+template <int MAXR, int CHUNK, int COLS>
+__global__ void __launch_bounds__(COLS * 16)
 ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ dtv, const float* __restrict__ d_skip,
                       float* state, long long slot_stride, float* __restrict__ y, const int* __restrict__ cu_q_lens,
-                      const int* __restrict__ state_slots, int H, int G, int N, int P, int CH) {
-  extern __shared__ float stage[];          // [2][CHUNK][2 N + 8 + 2]
+                      const int* __restrict__ state_slots, int H, int G, int N, int P, int CH, int vec) {
+  extern __shared__ __align__(16) float stage[];   // [2][CHUNK][per], then part [CHUNK * COLS][17], skip [CHUNK * COLS]
   pdl_prologue(xbc, dtv, state);
-  const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * 8;
+  constexpr int THREADS = COLS * 16;
+  const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * COLS;
   const int g = h / (H / G);
   const int t0 = cu_q_lens[b], n_tok = cu_q_lens[b + 1] - t0;
   if (n_tok <= 0) return;
@@ -78,8 +81,11 @@ ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ 
   const int p = p0 + col;
   const bool has_col = p < P;
   const int inner = H * P;
-  const int per = 2 * N + 10;
+  const int per = (2 * N + COLS + 2 + 3) / 4 * 4;       // B [N], C [N], x [COLS], dt, decay; rows 16 bytes apart
+  float* part = stage + (size_t)2 * CHUNK * per;
+  float* skip = part + CHUNK * COLS * 17;
   float* srow = state + slot * slot_stride + (long long)h * N * P;
+  const bool full_cols = p0 + COLS <= P;
 
   float S[MAXR];
 #pragma unroll
@@ -91,15 +97,38 @@ ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ 
   auto load_chunk = [&](int first, int buf) {
     const int count = n_tok - first < CHUNK ? n_tok - first : CHUNK;
     float* base = stage + (size_t)buf * CHUNK * per;
-    for (int i = threadIdx.x; i < count * per; i += 128) {
-      const int k = i / per, e = i - k * per;
-      const long long t = t0 + first + k;
-      const float* src;
-      if (e < N) src = xbc + t * CH + inner + (long long)g * N + e;
-      else if (e < 2 * N) src = xbc + t * CH + inner + (long long)G * N + (long long)g * N + (e - N);
-      else if (e < 2 * N + 8) src = xbc + t * CH + (long long)h * P + (p0 + e - 2 * N < P ? p0 + e - 2 * N : P - 1);
-      else src = reinterpret_cast<const float*>(dtv + t * H + h) + (e - 2 * N - 8);
-      __pipeline_memcpy_async(base + i, src, 4);
+    if (vec) {
+      // 16-byte pieces: N / 4 of B, N / 4 of C, COLS / 4 of x (whole columns only), then dt and the decay (8 bytes)
+      const int nb = N / 4, nx = full_cols ? COLS / 4 : 0, pieces = 2 * nb + nx + 1;
+      for (int i = threadIdx.x; i < count * pieces; i += THREADS) {
+        const int k = i / pieces, e = i - k * pieces;
+        const long long t = t0 + first + k;
+        float* dst = base + k * per;
+        if (e < nb) __pipeline_memcpy_async(dst + 4 * e, xbc + t * CH + inner + (long long)g * N + 4 * e, 16);
+        else if (e < 2 * nb)
+          __pipeline_memcpy_async(dst + N + 4 * (e - nb), xbc + t * CH + inner + (long long)(G + g) * N + 4 * (e - nb), 16);
+        else if (e < 2 * nb + nx)
+          __pipeline_memcpy_async(dst + 2 * N + 4 * (e - 2 * nb), xbc + t * CH + (long long)h * P + p0 + 4 * (e - 2 * nb), 16);
+        else __pipeline_memcpy_async(dst + 2 * N + COLS, dtv + t * H + h, 8);
+      }
+      if (!full_cols)
+        for (int i = threadIdx.x; i < count * COLS; i += THREADS) {
+          const int k = i / COLS, c = i - k * COLS;
+          __pipeline_memcpy_async(base + k * per + 2 * N + c,
+                                  xbc + (long long)(t0 + first + k) * CH + (long long)h * P + (p0 + c < P ? p0 + c : P - 1), 4);
+        }
+    } else {
+      const int items = 2 * N + COLS + 2;
+      for (int i = threadIdx.x; i < count * items; i += THREADS) {
+        const int k = i / items, e = i - k * items;
+        const long long t = t0 + first + k;
+        const float* src;
+        if (e < N) src = xbc + t * CH + inner + (long long)g * N + e;
+        else if (e < 2 * N) src = xbc + t * CH + inner + (long long)(G + g) * N + (e - N);
+        else if (e < 2 * N + COLS) src = xbc + t * CH + (long long)h * P + (p0 + e - 2 * N < P ? p0 + e - 2 * N : P - 1);
+        else src = reinterpret_cast<const float*>(dtv + t * H + h) + (e - 2 * N - COLS);
+        __pipeline_memcpy_async(base + k * per + e, src, 4);
+      }
     }
     __pipeline_commit();
   };
@@ -117,9 +146,10 @@ ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ 
     __syncthreads();
     const int count = n_tok - first < CHUNK ? n_tok - first : CHUNK;
     const float* base = stage + (size_t)buf * CHUNK * per;
+#pragma unroll 2
     for (int k = 0; k < count; ++k) {
       const float* v = base + k * per;
-      const float x = v[2 * N + col], dt = v[2 * N + 8], decay = v[2 * N + 9];
+      const float x = v[2 * N + col], dt = v[2 * N + COLS], decay = v[2 * N + COLS + 1];
       const float dtx = __fmul_rn(dt, x);
       float acc = 0.f;
 #pragma unroll
@@ -130,13 +160,18 @@ ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ 
           acc = __fmaf_rn(S[r], v[N + n], acc);
         }
       }
-      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
-      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
-      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-      if (lane == 0 && has_col) y[(long long)(t0 + first + k) * inner + (long long)h * P + p] = __fmaf_rn(dh, x, acc);
+      part[(k * COLS + col) * 17 + lane] = acc;
+      if (lane == 0) skip[k * COLS + col] = __fmul_rn(dh, x);
     }
-    __syncthreads();       // the buffer is written again a chunk on
+    __syncthreads();       // the shares are complete; the buffer may be written again a chunk on
+    for (int i = threadIdx.x; i < count * COLS; i += THREADS) {
+      const int k = i / COLS, c = i - k * COLS;
+      const float* ps = part + i * 17;
+      float acc = ps[0];
+#pragma unroll
+      for (int l = 1; l < 16; ++l) acc = __fadd_rn(acc, ps[l]);
+      if (p0 + c < P) y[(long long)(t0 + first + k) * inner + (long long)h * P + p0 + c] = __fadd_rn(acc, skip[i]);
+    }
   }
   if (slot != 0 && has_col) {
 #pragma unroll
@@ -170,20 +205,23 @@ ssm_output_kernel(const float* __restrict__ y, Source proj, long long row_width,
   }
 }
 
-template <int MAXR, int CHUNK>
+template <int MAXR, int CHUNK, int COLS>
 int launch_ssm_recurrence(const float* xbc, const float2* dtv, const float* d_skip, float* state, long long slot_stride,
                           float* y, const int* cu_q_lens, const int* state_slots, int B, int H, int G, int N, int P,
                           int CH, cudaStream_t st) {
-  const size_t smem = sizeof(float) * 2 * CHUNK * (2 * (size_t)N + 10);
+  const int per = (2 * N + COLS + 2 + 3) / 4 * 4;
+  const size_t smem = sizeof(float) * (2 * (size_t)CHUNK * per + (size_t)CHUNK * COLS * 18);
   static DeviceOnce once;
   if (smem > 48 * 1024 && !once.done()) {
-    if (cudaFuncSetAttribute(ssm_recurrence_kernel<MAXR, CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ssm_recurrence_kernel<MAXR, CHUNK, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              100 * 1024) != cudaSuccess)
       return DIB_LAUNCH_FAILED;
     once.mark();
   }
-  dib_launch(ssm_recurrence_kernel<MAXR, CHUNK>, dim3(B, H, (P + 7) / 8), dim3(128), smem, st, xbc, dtv, d_skip, state,
-             slot_stride, y, cu_q_lens, state_slots, H, G, N, P, CH);
+  // whole 16-byte pieces where every run starts on a 16-byte boundary
+  const int vec = (N % 4 == 0 && P % 4 == 0 && CH % 4 == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0) ? 1 : 0;
+  dib_launch(ssm_recurrence_kernel<MAXR, CHUNK, COLS>, dim3(B, H, (P + COLS - 1) / COLS), dim3(COLS * 16), smem, st, xbc,
+             dtv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, H, G, N, P, CH, vec);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -220,8 +258,13 @@ int dib_ssm_recurrence(const float* xbc, const float* dtv, const float* d_skip, 
   if (H < 1 || H > 65535 || G < 1 || H % G || N < 1 || N > 256 || P < 1 || (P + 7) / 8 > 65535) return DIB_BAD_SIZE;
   const int CH = H * P + 2 * G * N;
   const float2* dv = reinterpret_cast<const float2*>(dtv);
-#define DIB_SSM(MAXR, CHUNK) \
-  return launch_ssm_recurrence<MAXR, CHUNK>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, B, H, G, N, P, CH, st)
+  // blocks of 4 columns where blocks of 8 would leave SMs with less than two of them (the sums are the same)
+  const bool narrow = (long long)B * H * ((P + 7) / 8) < 2 * 148 && P > 4;
+#define DIB_SSM(MAXR, CHUNK)                                                                                          \
+  return narrow ? launch_ssm_recurrence<MAXR, CHUNK, 4>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, \
+                                                        B, H, G, N, P, CH, st)                                         \
+                : launch_ssm_recurrence<MAXR, CHUNK, 8>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, \
+                                                        B, H, G, N, P, CH, st)
   if (N <= 16) DIB_SSM(1, 16);
   if (N <= 32) DIB_SSM(2, 16);
   if (N <= 64) DIB_SSM(4, 16);

@@ -19,7 +19,7 @@ from tests import bovitar_util as bu
 from tests import plain_bovitar as pb
 
 QUERY, MARKS = 0, (1, 2, 3, 4, 5, 6)       # token ids 0..7 are the marked ones
-CLOSE_CALL = 0.02      # a bfloat16 engine may choose another expert where choice scores are this close
+CLOSE_CALL = 0.05      # a bfloat16 engine may choose another expert where choice scores are this close
 
 
 def row_errors(got, want):

@@ -255,19 +255,20 @@ def expert(h, w, p, rnd=_keep):
 def route_gap(h, w, p, r, ids):
     """How far a given choice ``ids`` [n, top] is from the rule's own, per token, in units of the choice
     scores: the larger of (a) how far the worst group it uses lies below the rule's worst kept group and
-    (b) how far its worst expert lies below the worst expert the rule would choose among the groups
-    that the rule keeps or the choice uses.  0 where the choice is the rule's."""
+    (b) how far its worst expert lies below the worst expert the rule would choose among the groups the
+    choice must have kept (the groups it uses, filled up with the best of the others).  0 where the
+    choice is the rule's."""
     experts, top = r["experts"], r["top"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
     n, per = h.shape[0], experts // groups["count"]
     choice = torch.softmax(h @ w[p + "router"].T, dim=-1) + w[p + "correction"]
     gscore = choice.reshape(n, groups["count"], per).max(-1).values
     kept_worst = gscore.topk(groups["keep"], dim=-1).values.min(-1).values
-    used_worst = gscore.gather(1, ids // per).min(-1).values
-    allowed = torch.zeros(n, groups["count"], dtype=torch.bool)
-    allowed.scatter_(1, gscore.topk(groups["keep"], dim=-1).indices, True)
-    allowed.scatter_(1, ids // per, True)
-    masked = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
+    used = torch.zeros(n, groups["count"], dtype=torch.bool).scatter_(1, ids // per, True)
+    used_worst = gscore.masked_fill(~used, math.inf).min(-1).values
+    kept = torch.zeros(n, groups["count"], dtype=torch.bool)
+    kept.scatter_(1, gscore.masked_fill(used, math.inf).topk(groups["keep"], dim=-1).indices, True)
+    masked = choice.masked_fill(~kept.repeat_interleave(per, dim=1), -math.inf)
     own = masked.topk(top, dim=-1).values.min(-1).values
     return torch.maximum(kept_worst - used_worst, own - choice.gather(1, ids).min(-1).values).clamp(min=0.0)
 
