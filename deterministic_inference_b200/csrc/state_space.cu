@@ -56,41 +56,42 @@ ssm_prepare_kernel(Source proj, long long row_width, const float* __restrict__ c
     }
 }
 
-// grid (B, H, ceil(P / COLS)), COLS * 16 threads: COLS columns of the head's state, a column's N rows
-// over 16 lanes (row n on lane n % 16, so MAXR = ceil(N / 16) rows a lane, kept in registers).  The
+// grid (B, H, ceil(P / COLS)), COLS * LANES threads: COLS columns of the head's state, a column's N rows
+// over LANES lanes (16 or 32; row n on lane n % LANES, so MAXR = ceil(N / LANES) rows a lane, kept in
+// registers).  The
 // sequence's tokens are walked in chunks of CHUNK tokens whose vectors (B and C of the head's group,
 // the x of the block's columns, dt and the decay) are staged in shared memory by cp.async (16 bytes
 // at a time where the sizes allow), one chunk ahead of the arithmetic.  A lane adds its rows'
 // share of a column's read-out in ascending order and leaves it in shared memory; once the chunk
-// is through, a thread per (token, column) adds the 16 lanes' shares in lane order: the order
-// depends on N alone, not on COLS, the chunk or the step.
-template <int MAXR, int CHUNK, int COLS>
-__global__ void __launch_bounds__(COLS * 16)
+// is through, a thread per (token, column) adds the lanes' shares in lane order: the order
+// depends on N alone (which decides LANES), not on COLS, the chunk or the step.
+template <int MAXR, int CHUNK, int COLS, int LANES>
+__global__ void __launch_bounds__(COLS * LANES)
 ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ dtv, const float* __restrict__ d_skip,
                       float* state, long long slot_stride, float* __restrict__ y, const int* __restrict__ cu_q_lens,
                       const int* __restrict__ state_slots, int H, int G, int N, int P, int CH, int vec) {
-  extern __shared__ __align__(16) float stage[];   // [2][CHUNK][per], then part [CHUNK * COLS][17], skip [CHUNK * COLS]
+  extern __shared__ __align__(16) float stage[];   // [2][CHUNK][per], then part [CHUNK * COLS][LANES + 1], skip [CHUNK * COLS]
   pdl_prologue(xbc, dtv, state);
-  constexpr int THREADS = COLS * 16;
+  constexpr int THREADS = COLS * LANES;
   const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * COLS;
   const int g = h / (H / G);
   const int t0 = cu_q_lens[b], n_tok = cu_q_lens[b + 1] - t0;
   if (n_tok <= 0) return;
   const long long slot = state_slots[b];
-  const int col = threadIdx.x >> 4, lane = threadIdx.x & 15;
+  const int col = threadIdx.x / LANES, lane = threadIdx.x % LANES;
   const int p = p0 + col;
   const bool has_col = p < P;
   const int inner = H * P;
   const int per = (2 * N + COLS + 2 + 3) / 4 * 4;       // B [N], C [N], x [COLS], dt, decay; rows 16 bytes apart
   float* part = stage + (size_t)2 * CHUNK * per;
-  float* skip = part + CHUNK * COLS * 17;
+  float* skip = part + CHUNK * COLS * (LANES + 1);
   float* srow = state + slot * slot_stride + (long long)h * N * P;
   const bool full_cols = p0 + COLS <= P;
 
   float S[MAXR];
 #pragma unroll
   for (int r = 0; r < MAXR; ++r) {
-    const int n = lane + 16 * r;
+    const int n = lane + LANES * r;
     S[r] = (slot != 0 && has_col && n < N) ? srow[(long long)n * P + p] : 0.f;
   }
 
@@ -146,37 +147,53 @@ ssm_recurrence_kernel(const float* __restrict__ xbc, const float2* __restrict__ 
     __syncthreads();
     const int count = n_tok - first < CHUNK ? n_tok - first : CHUNK;
     const float* base = stage + (size_t)buf * CHUNK * per;
-#pragma unroll 2
-    for (int k = 0; k < count; ++k) {
-      const float* v = base + k * per;
+    // one token: the state's rows move on, and the lane's share of the column's read-out
+    auto token = [&](const float* v) {
       const float x = v[2 * N + col], dt = v[2 * N + COLS], decay = v[2 * N + COLS + 1];
       const float dtx = __fmul_rn(dt, x);
       float acc = 0.f;
 #pragma unroll
       for (int r = 0; r < MAXR; ++r) {
-        const int n = lane + 16 * r;
+        const int n = lane + LANES * r;
         if (n < N) {
           S[r] = __fmaf_rn(v[n], dtx, __fmul_rn(decay, S[r]));
           acc = __fmaf_rn(S[r], v[N + n], acc);
         }
       }
-      part[(k * COLS + col) * 17 + lane] = acc;
-      if (lane == 0) skip[k * COLS + col] = __fmul_rn(dh, x);
+      return acc;
+    };
+    if (count == CHUNK) {
+      // a whole chunk: the shares stay in registers until the chunk is through, so that no store to
+      // shared memory stands between one token's loads and the next one's
+      float accs[CHUNK];
+#pragma unroll
+      for (int k = 0; k < CHUNK; ++k) accs[k] = token(base + k * per);
+#pragma unroll
+      for (int k = 0; k < CHUNK; ++k) {
+        part[(k * COLS + col) * (LANES + 1) + lane] = accs[k];
+        if (lane == 0) skip[k * COLS + col] = __fmul_rn(dh, base[k * per + 2 * N + col]);
+      }
+    } else {
+      for (int k = 0; k < count; ++k) {
+        const float acc = token(base + k * per);
+        part[(k * COLS + col) * (LANES + 1) + lane] = acc;
+        if (lane == 0) skip[k * COLS + col] = __fmul_rn(dh, base[k * per + 2 * N + col]);
+      }
     }
     __syncthreads();       // the shares are complete; the buffer may be written again a chunk on
     for (int i = threadIdx.x; i < count * COLS; i += THREADS) {
       const int k = i / COLS, c = i - k * COLS;
-      const float* ps = part + i * 17;
+      const float* ps = part + i * (LANES + 1);
       float acc = ps[0];
 #pragma unroll
-      for (int l = 1; l < 16; ++l) acc = __fadd_rn(acc, ps[l]);
+      for (int l = 1; l < LANES; ++l) acc = __fadd_rn(acc, ps[l]);
       if (p0 + c < P) y[(long long)(t0 + first + k) * inner + (long long)h * P + p0 + c] = __fadd_rn(acc, skip[i]);
     }
   }
   if (slot != 0 && has_col) {
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) {
-      const int n = lane + 16 * r;
+      const int n = lane + LANES * r;
       if (n < N) srow[(long long)n * P + p] = S[r];
     }
   }
@@ -205,22 +222,22 @@ ssm_output_kernel(const float* __restrict__ y, Source proj, long long row_width,
   }
 }
 
-template <int MAXR, int CHUNK, int COLS>
+template <int MAXR, int CHUNK, int COLS, int LANES>
 int launch_ssm_recurrence(const float* xbc, const float2* dtv, const float* d_skip, float* state, long long slot_stride,
                           float* y, const int* cu_q_lens, const int* state_slots, int B, int H, int G, int N, int P,
                           int CH, cudaStream_t st) {
   const int per = (2 * N + COLS + 2 + 3) / 4 * 4;
-  const size_t smem = sizeof(float) * (2 * (size_t)CHUNK * per + (size_t)CHUNK * COLS * 18);
+  const size_t smem = sizeof(float) * (2 * (size_t)CHUNK * per + (size_t)CHUNK * COLS * (LANES + 2));
   static DeviceOnce once;
   if (smem > 48 * 1024 && !once.done()) {
-    if (cudaFuncSetAttribute(ssm_recurrence_kernel<MAXR, CHUNK, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ssm_recurrence_kernel<MAXR, CHUNK, COLS, LANES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              100 * 1024) != cudaSuccess)
       return DIB_LAUNCH_FAILED;
     once.mark();
   }
   // whole 16-byte pieces where every run starts on a 16-byte boundary
   const int vec = (N % 4 == 0 && P % 4 == 0 && CH % 4 == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0) ? 1 : 0;
-  dib_launch(ssm_recurrence_kernel<MAXR, CHUNK, COLS>, dim3(B, H, (P + COLS - 1) / COLS), dim3(COLS * 16), smem, st, xbc,
+  dib_launch(ssm_recurrence_kernel<MAXR, CHUNK, COLS, LANES>, dim3(B, H, (P + COLS - 1) / COLS), dim3(COLS * LANES), smem, st, xbc,
              dtv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, H, G, N, P, CH, vec);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
@@ -258,18 +275,19 @@ int dib_ssm_recurrence(const float* xbc, const float* dtv, const float* d_skip, 
   if (H < 1 || H > 65535 || G < 1 || H % G || N < 1 || N > 256 || P < 1 || (P + 7) / 8 > 65535) return DIB_BAD_SIZE;
   const int CH = H * P + 2 * G * N;
   const float2* dv = reinterpret_cast<const float2*>(dtv);
-  // blocks of 4 columns where blocks of 8 would leave SMs with less than two of them (the sums are the same)
+  // blocks of 4 columns where blocks of 8 would leave SMs with less than two of them (the sums are the same);
+  // a column's rows over 32 lanes from a state of 64 on
   const bool narrow = (long long)B * H * ((P + 7) / 8) < 2 * 148 && P > 4;
-#define DIB_SSM(MAXR, CHUNK)                                                                                          \
-  return narrow ? launch_ssm_recurrence<MAXR, CHUNK, 4>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, \
-                                                        B, H, G, N, P, CH, st)                                         \
-                : launch_ssm_recurrence<MAXR, CHUNK, 8>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens, state_slots, \
-                                                        B, H, G, N, P, CH, st)
-  if (N <= 16) DIB_SSM(1, 16);
-  if (N <= 32) DIB_SSM(2, 16);
-  if (N <= 64) DIB_SSM(4, 16);
-  if (N <= 128) DIB_SSM(8, 16);
-  DIB_SSM(16, 8);
+#define DIB_SSM(MAXR, CHUNK, LANES)                                                                                  \
+  return narrow ? launch_ssm_recurrence<MAXR, CHUNK, 4, LANES>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens,       \
+                                                               state_slots, B, H, G, N, P, CH, st)                      \
+                : launch_ssm_recurrence<MAXR, CHUNK, 8, LANES>(xbc, dv, d_skip, state, slot_stride, y, cu_q_lens,       \
+                                                               state_slots, B, H, G, N, P, CH, st)
+  if (N <= 16) DIB_SSM(1, 16, 16);
+  if (N <= 32) DIB_SSM(2, 16, 16);
+  if (N <= 64) DIB_SSM(2, 16, 32);
+  if (N <= 128) DIB_SSM(4, 16, 32);
+  DIB_SSM(8, 8, 32);
 #undef DIB_SSM
 }
 

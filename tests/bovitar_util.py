@@ -81,12 +81,12 @@ CONFIGS = {
     "b2": dict(page_size=32, seed=62, config={
         "architecture": "Bovitar", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
         "layers": [delta(2, 2, 32, 32, 1, mlp=moe(4, 1, 48, 1.0, groups=(1, 1), shared=64)),
-                   parallel(attention(1, 1, 48, 48, 1, 48, 20000.0),
+                   parallel(attention(1, 1, 48, 48, 1, 48, 30000.0),
                             state_space(1, 40, 16, 1, 1, 1), mlp=moe(3, 3, 40, 3.0, shared=24))]}),
     # sizes the tensor-core kernels take; many experts in groups; a group per state-space head; two
     # layers that run twice, in another order than their owners; pages of 8
     "b3": dict(page_size=8, seed=63, config={
-        "architecture": "Bovitar", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
+        "architecture": "Bovitar", "vocab": 211, "width": 128, "norm": {"eps": 3e-6}, "logit_scale": 0.3,
         "layers": _with_repeats([
             delta(4, 4, 128, 64, 2, mlp=moe(32, 4, 64, 2.5, groups=(8, 3), shared=128)),
             parallel(attention(8, 2, 64, 32, 2, 32, 10000.0, scaling=(8.0, 1.0, 4.0, 64), softcap=30.0),
