@@ -272,7 +272,7 @@ int dib_ssm_recurrence(const float* xbc, const float* dtv, const float* d_skip, 
                        float* y, const int* cu_q_lens, const int* state_slots, int B, int H, int G, int N, int P,
                        cudaStream_t st) {
   if (B == 0) return DIB_OK;
-  if (H < 1 || H > 65535 || G < 1 || H % G || N < 1 || N > 256 || P < 1 || (P + 7) / 8 > 65535) return DIB_BAD_SIZE;
+  if (H < 1 || H > 65535 || G < 1 || H % G || N < 1 || N > 512 || P < 1 || (P + 7) / 8 > 65535) return DIB_BAD_SIZE;
   const int CH = H * P + 2 * G * N;
   const float2* dv = reinterpret_cast<const float2*>(dtv);
   // blocks of 4 columns where blocks of 8 would leave SMs with less than two of them (the sums are the same);
@@ -287,7 +287,8 @@ int dib_ssm_recurrence(const float* xbc, const float* dtv, const float* d_skip, 
   if (N <= 32) DIB_SSM(2, 16, 16);
   if (N <= 64) DIB_SSM(2, 16, 32);
   if (N <= 128) DIB_SSM(4, 16, 32);
-  DIB_SSM(8, 8, 32);
+  if (N <= 256) DIB_SSM(8, 8, 32);
+  DIB_SSM(16, 4, 32);
 #undef DIB_SSM
 }
 

@@ -1213,7 +1213,7 @@ def state_space(proj, conv_weight: torch.Tensor, conv_bias, a_log: torch.Tensor,
     st = lib.dib_ssm_recurrence(_ptr(xbc), _ptr(dtv), _ptr(d_skip), _ptr(state), c_longlong(slot_stride), _ptr(y),
                                 _ptr(step.cu_q_lens), _ptr(step.state_slots), c_int(step.num_seqs), c_int(h),
                                 c_int(g), c_int(n), c_int(p), _stream())
-    _check(st, "state_space(recurrence)", f"state {n} (at most 256)")
+    _check(st, "state_space(recurrence)", f"state {n} (at most 512)")
     out = torch.empty(t, inner, dtype=out_dtype, device=dev)
     st = lib.dib_ssm_output(_ptr(y), *src, c_longlong(width), _ptr(norm_weight), _ptr(out), c_int(_DT[out_dtype]),
                             _ptr(state), c_longlong(slot_stride), c_longlong(tail_at), _ptr(step.cu_q_lens),

@@ -110,7 +110,7 @@ class _Step:
 
 
 @pytest.mark.parametrize("heads, pdim, state, groups, parts, taps", [
-    (8, 64, 128, 2, 2, 4), (3, 20, 24, 3, 1, 2), (16, 32, 64, 1, 4, 4), (2, 12, 256, 2, 2, 1)])
+    (8, 64, 128, 2, 2, 4), (3, 20, 24, 3, 1, 2), (16, 32, 64, 1, 4, 4), (2, 12, 256, 2, 2, 1), (2, 8, 300, 1, 1, 2)])
 def test_the_state_space_kernels_alone(heads, pdim, state, groups, parts, taps):
     """Sequences of unequal lengths in one launch, then their next tokens from the state the launch
     left, against the plain recurrence over the whole sequences."""
